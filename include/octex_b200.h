@@ -1,0 +1,254 @@
+/* C interface of the B200 search library.
+ *
+ * The cuvsOctex* functions, structs and enums below are the ones a program written against the
+ * reference's C API binds (hpdic/octex, c/include/cuvs/neighbors/octex.h): same names, field
+ * order, defaults, ownership and error conventions. The few cuvs* functions the reference takes
+ * from the cuVS C library (resources, stream, last error text) are provided too, so that this one
+ * shared library satisfies such a program. The octexB200* functions are the same operations with
+ * plain pointers and sizes, for callers without DLPack (ctypes, cgo, JNI).
+ *
+ * Every function returns CUVS_SUCCESS or CUVS_ERROR; after CUVS_ERROR, cuvsGetLastErrorText()
+ * returns the message of the failing call on this thread (c/src/core/exceptions.hpp:17-33).
+ */
+#ifndef OCTEX_B200_H_
+#define OCTEX_B200_H_
+
+#include <stdbool.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define OCTEX_B200_EXPORT __attribute__((visibility("default")))
+
+/* ---- what the reference takes from cuVS's C library (cuvs/core/c_api.h) ---- */
+
+typedef enum { CUVS_ERROR = 0, CUVS_SUCCESS = 1 } cuvsError_t;
+typedef uintptr_t cuvsResources_t;
+
+OCTEX_B200_EXPORT cuvsError_t cuvsResourcesCreate(cuvsResources_t* res);
+OCTEX_B200_EXPORT cuvsError_t cuvsResourcesDestroy(cuvsResources_t res);
+/* stream: a cudaStream_t */
+OCTEX_B200_EXPORT cuvsError_t cuvsStreamSet(cuvsResources_t res, void* stream);
+OCTEX_B200_EXPORT cuvsError_t cuvsStreamGet(cuvsResources_t res, void** stream);
+OCTEX_B200_EXPORT cuvsError_t cuvsStreamSync(cuvsResources_t res);
+OCTEX_B200_EXPORT const char* cuvsGetLastErrorText(void);
+OCTEX_B200_EXPORT void cuvsSetLastErrorText(const char* text);
+
+/* ---- DLPack v1.0 tensor structs, declared here only if dlpack/dlpack.h was not included ---- */
+#ifndef DLPACK_DLPACK_H_
+#define OCTEX_B200_OWN_DLPACK 1
+typedef enum {
+  kDLCPU = 1, kDLCUDA = 2, kDLCUDAHost = 3, kDLCUDAManaged = 13
+} DLDeviceType;
+typedef struct { DLDeviceType device_type; int32_t device_id; } DLDevice;
+typedef enum { kDLInt = 0U, kDLUInt = 1U, kDLFloat = 2U } DLDataTypeCode;
+typedef struct { uint8_t code; uint8_t bits; uint16_t lanes; } DLDataType;
+typedef struct {
+  void* data;
+  DLDevice device;
+  int32_t ndim;
+  DLDataType dtype;
+  int64_t* shape;
+  int64_t* strides; /* in elements; NULL: compact row-major */
+  uint64_t byte_offset;
+} DLTensor;
+typedef struct DLManagedTensor {
+  DLTensor dl_tensor;
+  void* manager_ctx;
+  void (*deleter)(struct DLManagedTensor* self);
+} DLManagedTensor;
+#endif
+
+/* ---- index build parameters: c/include/cuvs/neighbors/octex.h:31-76 ---- */
+
+struct cuvsOctexIndexParams {
+  int32_t copies;
+  int32_t blocks;
+  int32_t pca_dims;
+  const float* spacings;
+  int32_t n_spacings;
+  int32_t list_len;
+  int32_t min_cell;
+  int32_t log_buckets;
+  int32_t sketch_width;
+  int32_t table_len;
+  bool reverse_edges;
+  bool exact_lists;
+  int32_t list_probes;
+  bool member_lists;
+  int64_t exact_table_max;
+  int32_t table_passes;
+  bool table_sketch_order;
+  bool write_behind;
+  uint64_t seed;
+  const int32_t* devices;
+  int32_t n_devices;
+};
+typedef struct cuvsOctexIndexParams* cuvsOctexIndexParams_t;
+/* octex.h:81-84 */
+OCTEX_B200_EXPORT cuvsError_t cuvsOctexIndexParamsCreate(cuvsOctexIndexParams_t* params);
+OCTEX_B200_EXPORT cuvsError_t cuvsOctexIndexParamsDestroy(cuvsOctexIndexParams_t params);
+
+/* ---- load parameters: octex.h:96-140 ---- */
+
+typedef enum { OCTEX_PLACEMENT_REPLICATE = 0, OCTEX_PLACEMENT_SHARD = 1 } cuvsOctexPlacement;
+typedef enum {
+  OCTEX_SKETCH_REPLICATE = 0, OCTEX_SKETCH_SHARD = 1, OCTEX_SKETCH_HOST = 2
+} cuvsOctexSketchPlacement;
+
+struct cuvsOctexLoadParams {
+  const int32_t* devices;
+  int32_t n_devices;
+  cuvsOctexPlacement placement;
+  bool vectors_on_host;
+  bool shard_vectors;
+  bool table_on_host;
+  cuvsOctexSketchPlacement sketch;
+  int32_t parts;
+  int32_t copies_per_part;
+  int32_t copies_limit;
+  int32_t list_limit;
+};
+typedef struct cuvsOctexLoadParams* cuvsOctexLoadParams_t;
+/* octex.h:146-149 */
+OCTEX_B200_EXPORT cuvsError_t cuvsOctexLoadParamsCreate(cuvsOctexLoadParams_t* params);
+OCTEX_B200_EXPORT cuvsError_t cuvsOctexLoadParamsDestroy(cuvsOctexLoadParams_t params);
+
+/* ---- search parameters: octex.h:161-184 ---- */
+
+struct cuvsOctexSearchParams {
+  int32_t read;
+  int32_t starts;
+  int32_t waves;
+  int32_t rerank;
+  int32_t wave_rerank;
+  int32_t batch;
+  bool sketch_rank;
+  int32_t final_rerank;
+  bool balanced_gather; /* accepted, ignored: one implementation */
+  bool fused_merge;     /* accepted, ignored */
+  bool use_graph;       /* accepted, ignored */
+};
+typedef struct cuvsOctexSearchParams* cuvsOctexSearchParams_t;
+/* octex.h:189-192 */
+OCTEX_B200_EXPORT cuvsError_t cuvsOctexSearchParamsCreate(cuvsOctexSearchParams_t* params);
+OCTEX_B200_EXPORT cuvsError_t cuvsOctexSearchParamsDestroy(cuvsOctexSearchParams_t params);
+
+/* ---- index handle: octex.h:204-240 ---- */
+
+typedef struct { uintptr_t addr; } cuvsOctexIndex;
+typedef cuvsOctexIndex* cuvsOctexIndex_t;
+
+OCTEX_B200_EXPORT cuvsError_t cuvsOctexIndexCreate(cuvsOctexIndex_t* index);
+OCTEX_B200_EXPORT cuvsError_t cuvsOctexIndexDestroy(cuvsOctexIndex_t index);
+OCTEX_B200_EXPORT cuvsError_t cuvsOctexIndexGetSize(cuvsOctexIndex_t index, int64_t* size);
+OCTEX_B200_EXPORT cuvsError_t cuvsOctexIndexGetDim(cuvsOctexIndex_t index, int64_t* dim);
+OCTEX_B200_EXPORT cuvsError_t cuvsOctexIndexGetCopies(cuvsOctexIndex_t index, int32_t* copies);
+OCTEX_B200_EXPORT cuvsError_t cuvsOctexIndexGetNumDevices(cuvsOctexIndex_t index, int32_t* n_devices);
+OCTEX_B200_EXPORT cuvsError_t cuvsOctexIndexGetDevices(cuvsOctexIndex_t index, int32_t* devices);
+OCTEX_B200_EXPORT cuvsError_t cuvsOctexIndexGetDeviceBytes(cuvsOctexIndex_t index, int64_t* bytes);
+
+/* ---- build, load, search: octex.h:261-295 ---- */
+
+/* The index builder is not part of this library (it covers the search path): returns CUVS_ERROR
+ * after the same argument checks as the reference. Directories come from the reference's builder
+ * or from the Python tooling of this repository. */
+OCTEX_B200_EXPORT cuvsError_t cuvsOctexBuild(cuvsResources_t res, cuvsOctexIndexParams_t params,
+                                             DLManagedTensor* dataset, const char* path);
+/* Load an index directory onto the GPU of this process into an empty handle (params NULL: the
+ * defaults). octex.h:268-271 */
+OCTEX_B200_EXPORT cuvsError_t cuvsOctexLoad(cuvsResources_t res, const char* path,
+                                            cuvsOctexLoadParams_t params, cuvsOctexIndex_t index);
+/* queries [n, dim] float32, neighbors [n, k] int64, distances [n, k] float32; all on the host or
+ * all on a device. Host results are written on return; device results are ordered on the stream
+ * of res. octex.h:290-295 */
+OCTEX_B200_EXPORT cuvsError_t cuvsOctexSearch(cuvsResources_t res, cuvsOctexSearchParams_t params,
+                                              cuvsOctexIndex_t index, DLManagedTensor* queries,
+                                              DLManagedTensor* neighbors, DLManagedTensor* distances);
+
+/* ---- the same operations with plain pointers ---- */
+
+/* cuvsOctexSearch (octex.h:290-295) without DLPack. on_device: 0 = the three arrays are host
+ * memory, 1 = device memory. */
+OCTEX_B200_EXPORT cuvsError_t octexB200Search(cuvsResources_t res, cuvsOctexSearchParams_t params,
+                                              cuvsOctexIndex_t index, const float* queries,
+                                              int64_t n_queries, int64_t dim, int64_t* neighbors,
+                                              float* distances, int64_t k, int32_t on_device);
+
+/* cuvsOctexLoad (octex.h:268-271) for one process per GPU: this process is `rank` of `world`
+ * processes that share the index (shard placement deals the copies over the processes as
+ * cpp/src/neighbors/octex/load.cu:264-281 deals them over GPUs). */
+OCTEX_B200_EXPORT cuvsError_t octexB200LoadRank(cuvsResources_t res, const char* path,
+                                                cuvsOctexLoadParams_t params, int32_t rank,
+                                                int32_t world, cuvsOctexIndex_t index);
+
+/* The arrays of an index directory handed over in memory (host or device pointers), with the
+ * dtypes and shapes of docs/design.md:27-48. */
+typedef struct {
+  int64_t n, dim;
+  int32_t copies, blocks, list_len, log_buckets, sketch_width, table_len;
+  const float* spacings;
+  int32_t n_spacings;
+  int32_t borrow; /* 1: device arrays needing no re-layout are used in place, not copied */
+  int64_t stride; /* entries per copy in lists */
+  int64_t mmax;   /* keys per (copy, level) */
+  const float* mean;
+  const float* proj;
+  const float* shift;
+  const int32_t* lists;
+  const int64_t* keys;
+  const int32_t* offsets;
+  const int32_t* base;
+  const float* sketch_basis;
+  const float* sketch_scale;
+  const int8_t* sketch;
+  const void* vectors; /* fp16 */
+  const int32_t* table;
+} octexB200Arrays;
+
+/* cuvsOctexLoad from memory instead of a directory (the reference has no such call; its loader is
+ * cpp/src/neighbors/octex/load.cu:206-494). */
+OCTEX_B200_EXPORT cuvsError_t octexB200Attach(cuvsResources_t res, const octexB200Arrays* arrays,
+                                              cuvsOctexLoadParams_t params, int32_t rank,
+                                              int32_t world, cuvsOctexIndex_t index);
+
+/* detail::resident_search (cpp/src/neighbors/octex/search.cu:983-997): search again the queries of
+ * the previous call, which are still on the GPU, and leave the results there. The timing protocol
+ * of the reference's benchmark uses it (cpp/bench/octex_bench.cu:223-253). */
+OCTEX_B200_EXPORT cuvsError_t octexB200SearchResident(cuvsResources_t res,
+                                                      cuvsOctexSearchParams_t params,
+                                                      cuvsOctexIndex_t index, int64_t n_queries,
+                                                      int64_t k);
+
+/* detail::timed_batch (search.cu:965-981) per kernel: one batch of the queries already on the GPU,
+ * launched kernel by kernel with events between them. ms receives the milliseconds of centre +
+ * sketch query, projection, cell codes, cell lookup, first round, each wave, best k; *count their
+ * number. */
+OCTEX_B200_EXPORT cuvsError_t octexB200ProfileBatch(cuvsResources_t res,
+                                                    cuvsOctexSearchParams_t params,
+                                                    cuvsOctexIndex_t index, int64_t n_queries,
+                                                    int64_t k, float* ms, int32_t capacity,
+                                                    int32_t* count);
+
+/* Observation (detail::timed_batch / memory_report, search.cu:965-1016, are the reference's
+ * counterparts): stats = per-query counters of what the kernels read, taps = keep the intermediate
+ * arrays of the last batch. Either one changes the plan; both are off by default. */
+OCTEX_B200_EXPORT cuvsError_t octexB200SetDebug(cuvsOctexIndex_t index, int32_t stats, int32_t taps);
+/* Copy a named array of the last batch to host memory: "y", "qs", "codes", "seg", "cand1",
+ * "cand1_dist", "n1", "kept1_ids", "kept1_dist", "stats", "kept_ids", "kept_dist". *bytes returns
+ * its size; dst may be NULL to ask for the size only. */
+OCTEX_B200_EXPORT cuvsError_t octexB200Fetch(cuvsOctexIndex_t index, const char* name, void* dst,
+                                             int64_t capacity, int64_t* bytes);
+
+/* Cell codes of n rows of 8 * blocks float32 coordinates scaled by inv_f, computed on the GPU by
+ * the device function every search kernel uses (e8b_hash64 of
+ * cpp/src/neighbors/octex/detail/e8.cuh:66-85). Host pointers. */
+OCTEX_B200_EXPORT cuvsError_t octexB200CellCodes(const float* y, int64_t n, int32_t blocks,
+                                                 float inv_f, int64_t* codes);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* OCTEX_B200_H_ */

@@ -1,0 +1,89 @@
+// The index as the search kernels read it: arrays of one process's GPU and their layout.
+//
+// Layout (the reference's is in cpp/src/neighbors/octex/detail/index_impl.hpp:115-177 of
+// hpdic/octex; differences are marked *):
+//   lists   i32 [Cg, stride]     cell rows of list_len ids, nearest to the cell centre first
+//   keys    i64 [Cg, L, mmax]    cell codes in (bucket, code) order
+//   offsets i32 [Cg, L, T + 1]   CSR bounds of the buckets into keys
+//   base    i32 [Cg, L]          first list row of a level inside the copy
+// * ut      f16 [Cg * 8b, ldu]   projections, one row per projected coordinate, K-major
+//                                (ldu = dim rounded up to 64, zero padded): the operand layout of
+//                                the tensor-core projection (the reference keeps [dim, Cg * 8b])
+//   shift   f16 [Cg * 8b]        inv_f f32 [L]     mean f32 [dim]
+//   basis   f32 [dim, S]         scale f32 [S]     sketch i8 [n, S]
+//   vectors f16 [n, dim]         table i32 [n, table_len]
+// * level_on u8 [Cg, L]          1 when the level of the copy holds at least one cell
+#pragma once
+
+#include "common.hpp"
+
+#include <octex_b200.hpp>
+
+#include <map>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <vector>
+
+namespace octex_b200::detail {
+
+struct plan;
+
+/// Observation switches of an index (off in normal use; tests and the benchmark's byte
+/// accounting turn them on). Changing them rebuilds the plan.
+struct debug_options {
+  bool stats = false;  ///< per-query counters of what the kernels read
+  bool taps  = false;  ///< keep the intermediate arrays of the last batch for inspection
+};
+
+struct device_part {
+  int device     = 0;
+  int copies     = 0;  // copies held by this process
+  int copy0      = 0;  // first of them
+  int64_t stride = 0;
+  int64_t mmax   = 0;
+  int ldu        = 0;
+  dbuf lists, keys, offsets, base, ut, shift, inv_f, mean, basis, scale, sketch, vectors, table,
+    level_on;
+  cudaStream_t stream = nullptr;
+  int64_t bytes       = 0;
+
+  device_part() = default;
+  device_part(device_part const&) = delete;
+  ~device_part()
+  {
+    if (stream != nullptr) {
+      int cur = 0;
+      cudaGetDevice(&cur);
+      cudaSetDevice(device);
+      cudaStreamDestroy(stream);
+      cudaSetDevice(cur);
+    }
+  }
+};
+
+struct index_impl {
+  std::string path;
+  load_params params;
+  int64_t n = 0, dim = 0;
+  int copies = 0;  // copies loaded over all processes
+  int blocks = 4, list_len = 0, log_buckets = 20, sketch_width = 0, table_len = 0;
+  std::vector<float> spacings;
+  std::vector<int> devices;
+  int rank = 0, world = 1;
+  device_part part;
+  std::mutex mu;  // guards plans
+  std::map<std::string, std::shared_ptr<plan>> plans;
+  debug_options debug;
+  ~index_impl();
+};
+
+/// Host-side view of the arrays of an index (directory or memory) that placement reads from.
+struct source_arrays {
+  index_arrays a;
+  int all_copies = 0;
+};
+
+void place(index_impl& ix, source_arrays const& src);
+
+}  // namespace octex_b200::detail

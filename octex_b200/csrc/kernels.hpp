@@ -1,0 +1,114 @@
+// Launch interface of the search kernels: plain pointers and sizes, one function per kernel.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace octex_b200::kernels {
+
+constexpr int kMinLogHash  = 11;     // smallest per-query hash set: 2^11 slots
+constexpr int kMaxHash     = 32768;  // largest per-query hash set
+constexpr int kMaxRerank   = 512;    // exact rerank depth per round
+constexpr int kMaxKeepSort = 1024;   // kept + reranked keys sorted together (exact ranking)
+constexpr int kMaxSketchKO = 1024;   // kept entries when ranking by sketch
+constexpr int kMaxExpanded = 6144;   // start points expanded by earlier waves
+constexpr int kRoundThreads = 256;
+
+/// Rows [from, m) of q become copies of row 0 (padding of a partial batch).
+void pad_rows(float* q, int from, int m, int D, cudaStream_t s);
+
+/// qh [m, ldq] = half(q - mean) zero-padded to ldq columns; qs [m, S] = (q - mean) @ basis in fp32
+/// (one fused multiply-add per dimension, in dimension order).
+void center_sketch(const float* q, const float* mean, const float* basis, int m, int D, int S,
+                   __half* qh, int ldq, float* qs, cudaStream_t s);
+
+/// Y [m, N] = half(fp32(qh . ut^T) + shift) with the dot product accumulated by one fused
+/// multiply-add per dimension in dimension order (the order of the CPU checker). ut is [N, ldu].
+void project_ordered(const __half* qh, int ldq, const __half* ut, int ldu, const __half* shift,
+                     int m, int N, int D, __half* Y, cudaStream_t s);
+
+/// codes [pairs, L] = cell code at every level of the 8*blocks coordinates of each (query, copy)
+/// pair of Y [pairs, 8*blocks]. level_on [C, L] (may be null) marks the levels that hold cells;
+/// the others get code 0 and are never looked at.
+void decode_codes(const __half* Y, int64_t pairs, int C, int blocks, int L, const float* inv_f,
+                  const unsigned char* level_on, long long* codes, cudaStream_t s);
+
+/// codes [n] = cell code of each row of y [n, 8*blocks] float32 scaled by inv_f.
+void cell_codes_f32(const float* y, int64_t n, int blocks, float inv_f, long long* codes,
+                    cudaStream_t s);
+
+/// seg [m, C] = (first list entry, entries read) of the finest level whose cell holds a list,
+/// (0, 0) when none does. stats (may be null) [m, 2] += (levels tried, keys scanned).
+void probe(const long long* codes, int m, int C, int L, const int* offsets, int64_t T1,
+           const long long* keys, int64_t mmax, const int* base, const unsigned char* level_on,
+           int list_len, int lr, int log_buckets, int2* seg, long long* stats, cudaStream_t s);
+
+/// One round of a query block: distinct ids of its segments, sketch distances, the R nearest by
+/// sketch reranked exactly (or the KO nearest kept by sketch distance), merged into the kept list.
+struct round_args {
+  int m = 0;     // queries = thread blocks
+  int nseg = 0;  // segments per query: copies (lists) or starts (table rows)
+  // lists mode: segment (start, len) into the lists of copy c
+  const int2* seg = nullptr;
+  const int* lists = nullptr;
+  int64_t stride = 0;
+  // rows mode: the first `starts` kept entries no earlier wave expanded; their table rows
+  const int* table = nullptr;
+  int table_len = 0;
+  int* done = nullptr;  // [m, done_stride] start points of all waves
+  int done_stride = 0;
+  int done_off = 0;  // entries of earlier waves
+  int pick_slots = 0;  // hash slots for the earlier start points (power of two)
+  // sketch
+  const signed char* sketch = nullptr;
+  const float* scale = nullptr;
+  const float* qs = nullptr;  // [m, sw]
+  int sw = 0;
+  // exact rerank
+  const __half* vectors = nullptr;
+  int D = 0;
+  const float* Q = nullptr;  // [m, D] uncentred queries
+  int R = 0;                 // rerank depth (exact) — ignored when sketch_rank
+  int KO = 0;
+  int sketch_rank = 0;
+  int fresh = 0;  // the kept list starts empty
+  long long* si = nullptr;  // kept ids [m, KO]
+  float* sd = nullptr;      // kept distances [m, KO]
+  // sizes of the shared-memory carve-up (host decides)
+  int ht_slots = 0;   // ints of the hash set region (>= largest set used, >= pick_slots)
+  int log_cap = 0;    // log2 of the largest gather hash set
+  int nmax = 0;       // capacity of the candidate / distance arrays
+  int P = 0;          // keys sorted by the merge (power of two >= KO + selected)
+  int* cand_global = nullptr;    // [m, nmax] when the candidates do not fit shared memory
+  float* dist_global = nullptr;  // [m, nmax]
+  // observation (all may be null)
+  int* tap_cand = nullptr;    // [m, tap_cap]
+  float* tap_dist = nullptr;  // [m, tap_cap]
+  int* tap_n = nullptr;       // [m]
+  int tap_cap = 0;
+  long long* stats = nullptr;  // [m, 8]: [2] entries read, [3] distinct ids first round,
+                               // [4] table rows expanded, [5] distinct ids of waves,
+                               // [6] rows reranked exactly
+};
+size_t round_smem_bytes(const round_args& a);
+void round_lists(const round_args& a, cudaStream_t s);
+void round_rows(const round_args& a, cudaStream_t s);
+/// Opt every round kernel in to `bytes` of dynamic shared memory on the current device.
+void round_allow_smem(size_t bytes);
+
+/// bi, bd [m, k] = the first k columns of si, sd [m, KO].
+void take_k(const long long* si, const float* sd, int KO, int k, int m, long long* bi, float* bd,
+            cudaStream_t s);
+
+/// Exact rerank of the first R kept entries (sketch ranking) into the best k.
+void final_rerank(const long long* si, int KO, int R, const __half* vectors, int D, const float* Q,
+                  int k, int m, long long* bi, float* bd, long long* stats, cudaStream_t s);
+
+/// Merge of nsrc kept lists [*, KO] (already in this GPU's memory, back to back: source h at
+/// src + h * src_stride): nearest copy of every id, best KO.
+void merge_kept(const long long* src_i, const float* src_d, int nsrc, int64_t src_stride, int KO,
+                int P, int m, long long* si, float* sd, cudaStream_t s);
+
+}  // namespace octex_b200::kernels

@@ -1,0 +1,418 @@
+// Batched search: plan (limits, buffers, one CUDA graph per batch shape) and the per-batch loop.
+//
+// Answers cpp/src/neighbors/octex/search.cu of hpdic/octex (make_plan :619-794, get_plan :796-814,
+// search_impl :816-961, the two search overloads :1020-1064) for one process per GPU. Parameter
+// limits and error texts are the reference's. A batch is: copy the queries in, pad a partial batch
+// with copies of its first row, replay the graph (centre + sketch-space query, projection, cell
+// codes, cell lookup, first round, waves, best k), copy the results out.
+
+#include "search_impl.hpp"
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+
+namespace octex_b200 {
+
+namespace detail {
+
+namespace {
+
+auto log2_ceil(int64_t v) -> int
+{
+  int e = 0;
+  while ((int64_t{1} << e) < v)
+    e++;
+  return e;
+}
+
+template <typename T>
+auto alloc(plan& pl, int device, int64_t count, int fill = -2) -> dbuf
+{
+  dbuf b(device, static_cast<size_t>(std::max<int64_t>(count, 1)) * sizeof(T));
+  if (fill != -2) OCTEX_CUDA_TRY(cudaMemset(b.ptr, fill, b.size));
+  pl.buffer_bytes += static_cast<int64_t>(b.size);
+  return b;
+}
+
+constexpr size_t kSmemSoftLimit = size_t{96} << 10;   // above this the candidates go to global memory
+constexpr size_t kSmemHardLimit = size_t{227} << 10;  // shared memory a block can opt in to
+
+/// Fill the size fields of a round and decide where its candidate arrays live.
+void size_round(plan& pl, kernels::round_args& r, int entries_max, int pick_entries, int device)
+{
+  r.log_cap = std::clamp(log2_ceil((3 * int64_t{entries_max} + 1) / 2), kernels::kMinLogHash,
+                         log2_ceil(kernels::kMaxHash));
+  r.pick_slots = 0;
+  if (pick_entries > 0) {
+    r.pick_slots = 64;
+    while (r.pick_slots * 3 < pick_entries * 4)  // at most 75 % full
+      r.pick_slots <<= 1;
+  }
+  r.ht_slots = std::max(1 << r.log_cap, r.pick_slots);
+  r.nmax     = std::max(entries_max, 1);
+  const int rm = r.sketch_rank ? r.KO : r.R;
+  r.P = 2;
+  while (r.P < r.KO + rm)
+    r.P <<= 1;
+  r.cand_global = nullptr;
+  r.dist_global = nullptr;
+  if (kernels::round_smem_bytes(r) > kSmemSoftLimit) {
+    // placeholders: non-null makes the layout drop the two arrays; the real buffers follow
+    r.cand_global = reinterpret_cast<int*>(1);
+    r.dist_global = reinterpret_cast<float*>(1);
+    OCTEX_EXPECTS(kernels::round_smem_bytes(r) <= kSmemHardLimit,
+                  "octex: the round does not fit shared memory");
+    pl.scratch_cand.push_back(alloc<int>(pl, device, int64_t{r.m} * r.nmax));
+    pl.scratch_dist.push_back(alloc<float>(pl, device, int64_t{r.m} * r.nmax));
+    r.cand_global = pl.scratch_cand.back().as<int>();
+    r.dist_global = pl.scratch_dist.back().as<float>();
+  }
+  pl.smem_max = std::max(pl.smem_max, kernels::round_smem_bytes(r));
+}
+
+}  // namespace
+
+plan::~plan()
+{
+  int cur = 0;
+  cudaGetDevice(&cur);
+  cudaSetDevice(device);
+  if (graph != nullptr) cudaGraphExecDestroy(graph);
+  if (done_ev != nullptr) cudaEventDestroy(done_ev);
+  cudaSetDevice(cur);
+}
+
+/// Launch every kernel of a batch on s (captured into the graph, or run directly).
+void run_batch(index_impl const& ix, plan& pl, cudaStream_t s, std::vector<cudaEvent_t>* marks)
+{
+  // marks (profiling only): one event before the first kernel and one after every kernel
+  auto mark = [&] {
+    if (marks == nullptr) return;
+    cudaEvent_t e = nullptr;
+    OCTEX_CUDA_TRY(cudaEventCreate(&e));
+    OCTEX_CUDA_TRY(cudaEventRecord(e, s));
+    marks->push_back(e);
+  };
+  auto const& p  = ix.part;
+  const int D    = static_cast<int>(ix.dim);
+  const int sw   = ix.sketch_width;
+  const int L    = static_cast<int>(ix.spacings.size());
+  const int wdt  = 8 * ix.blocks * p.copies;
+  const int64_t T1 = (int64_t{1} << ix.log_buckets) + 1;
+  if (pl.stats.ptr != nullptr) OCTEX_CUDA_TRY(cudaMemsetAsync(pl.stats.ptr, 0, pl.stats.size, s));
+  mark();
+  kernels::center_sketch(pl.qbuf.as<float>(), p.mean.as<float>(), p.basis.as<float>(), pl.m1, D, sw,
+                         pl.qh.as<__half>(), p.ldu, pl.qs.as<float>(), s);
+  mark();
+  kernels::project_ordered(pl.qh.as<__half>(), p.ldu, p.ut.as<__half>(), p.ldu,
+                           p.shift.as<__half>(), pl.m1, wdt, D, pl.Y.as<__half>(), s);
+  mark();
+  kernels::decode_codes(pl.Y.as<__half>(), int64_t{pl.m1} * p.copies, p.copies, ix.blocks, L,
+                        p.inv_f.as<float>(), pl.dbg.taps ? nullptr : p.level_on.as<unsigned char>(),
+                        pl.codes.as<long long>(), s);
+  mark();
+  kernels::probe(pl.codes.as<long long>(), pl.m1, p.copies, L, p.offsets.as<int>(), T1,
+                 p.keys.as<long long>(), p.mmax, p.base.as<int>(), p.level_on.as<unsigned char>(),
+                 ix.list_len, pl.lr, ix.log_buckets, pl.seg.as<int2>(), pl.stats.as<long long>(), s);
+  mark();
+  kernels::round_lists(pl.r1, s);
+  mark();
+  if (pl.dbg.taps) {
+    OCTEX_CUDA_TRY(cudaMemcpyAsync(pl.kept1_i.ptr, pl.si.ptr, pl.kept1_i.size, cudaMemcpyDeviceToDevice, s));
+    OCTEX_CUDA_TRY(cudaMemcpyAsync(pl.kept1_d.ptr, pl.sd.ptr, pl.kept1_d.size, cudaMemcpyDeviceToDevice, s));
+  }
+  for (int wv = 0; wv < pl.sp.waves; wv++) {
+    kernels::round_args r = pl.r2;
+    r.done_off            = wv * pl.sp.starts;
+    kernels::round_rows(r, s);
+    mark();
+  }
+  if (pl.sp.sketch_rank && pl.FR > 0) {
+    kernels::final_rerank(pl.si.as<long long>(), pl.KO, pl.FR, p.vectors.as<__half>(), D,
+                          pl.qbuf.as<float>(), pl.k, pl.m1, pl.bi.as<long long>(), pl.bd.as<float>(),
+                          pl.stats.as<long long>(), s);
+  } else {
+    kernels::take_k(pl.si.as<long long>(), pl.sd.as<float>(), pl.KO, pl.k, pl.m1,
+                    pl.bi.as<long long>(), pl.bd.as<float>(), s);
+  }
+  mark();
+  OCTEX_CUDA_TRY(cudaPeekAtLastError());
+}
+
+auto profile_batch(resources const& res, search_params const& sp, index const& idx, int64_t nq,
+                   int64_t k) -> std::vector<float>
+{
+  auto& ix = idx.impl();
+  OCTEX_EXPECTS(nq >= 1 && nq <= std::max(sp.batch, 1),
+                "octex: a profiled batch is one batch of queries already on the GPU");
+  (void)res;
+  auto pl = get_plan(ix, sp, static_cast<int>(nq), static_cast<int>(k));
+  std::lock_guard<std::mutex> lock(pl->mu);
+  int cur = 0;
+  OCTEX_CUDA_TRY(cudaGetDevice(&cur));
+  OCTEX_CUDA_TRY(cudaSetDevice(ix.part.device));
+  std::vector<cudaEvent_t> marks;
+  std::vector<float> ms;
+  try {
+    run_batch(ix, *pl, ix.part.stream, &marks);
+    OCTEX_CUDA_TRY(cudaStreamSynchronize(ix.part.stream));
+    for (size_t i = 1; i < marks.size(); i++) {
+      float t = 0.f;
+      OCTEX_CUDA_TRY(cudaEventElapsedTime(&t, marks[i - 1], marks[i]));
+      ms.push_back(t);
+    }
+  } catch (...) {
+    for (auto e : marks)
+      cudaEventDestroy(e);
+    cudaSetDevice(cur);
+    throw;
+  }
+  for (auto e : marks)
+    cudaEventDestroy(e);
+  OCTEX_CUDA_TRY(cudaSetDevice(cur));
+  return ms;
+}
+
+auto make_plan(index_impl& ix, search_params const& sp, int m, int k, debug_options dbg)
+  -> std::shared_ptr<plan>
+{
+  auto plp  = std::make_shared<plan>();
+  plan& pl  = *plp;
+  auto& p   = ix.part;
+  pl.sp     = sp;
+  pl.dbg    = dbg;
+  pl.m      = m;
+  pl.k      = k;
+  pl.KO     = std::max(sp.starts, k);
+  pl.lr     = std::min(sp.read, ix.list_len);
+  pl.R1     = sp.rerank;
+  pl.R2     = sp.wave_rerank;
+  pl.FR     = std::min(sp.final_rerank, pl.KO);
+  pl.device = p.device;
+  const int D  = static_cast<int>(ix.dim);
+  const int sw = ix.sketch_width;
+  const int S  = sp.starts;
+  const int L  = static_cast<int>(ix.spacings.size());
+  // search.cu:637-655
+  OCTEX_EXPECTS(sp.read >= 1 && sp.starts >= 1 && sp.waves >= 0,
+                "octex: read, starts >= 1 and waves >= 0");
+  OCTEX_EXPECTS(sp.waves == 0 || ix.table_len > 0, "octex: waves need the neighbor table");
+  OCTEX_EXPECTS(pl.KO <= (sp.sketch_rank ? kernels::kMaxSketchKO : kernels::kMaxRerank),
+                "octex: max(starts, k) must be <= 512 (1024 with sketch_rank)");
+  OCTEX_EXPECTS(sp.sketch_rank || (sp.rerank >= 1 && sp.rerank <= kernels::kMaxRerank &&
+                                   pl.KO + sp.rerank <= kernels::kMaxKeepSort),
+                "octex: rerank in [1, 512] and max(starts, k) + rerank <= 1024");
+  OCTEX_EXPECTS(sp.sketch_rank || sp.waves == 0 ||
+                  (sp.wave_rerank >= 1 && sp.wave_rerank <= kernels::kMaxRerank &&
+                   pl.KO + sp.wave_rerank <= kernels::kMaxKeepSort),
+                "octex: wave_rerank in [1, 512] and max(starts, k) + wave_rerank <= 1024");
+  OCTEX_EXPECTS(!sp.sketch_rank || pl.FR == 0 || (k <= pl.FR && pl.FR <= kernels::kMaxRerank),
+                "octex: final_rerank 0 (sketch order) or k <= final_rerank <= 512");
+  OCTEX_EXPECTS(sp.waves <= 1 || S * (sp.waves - 1) <= kernels::kMaxExpanded,
+                "octex: starts * (waves - 1) <= 6144");
+  OCTEX_EXPECTS(int64_t{p.copies} * pl.lr <= kernels::kMaxHash,
+                "octex: copies x read too large for the shared-memory hash set");
+  OCTEX_EXPECTS(sp.waves == 0 || int64_t{S} * ix.table_len <= kernels::kMaxHash,
+                "octex: starts x table_len too large for the shared-memory hash set");
+  OCTEX_EXPECTS(ix.world == 1, "octex: this plan serves a single process");
+  pl.m1 = m;
+
+  OCTEX_CUDA_TRY(cudaSetDevice(p.device));
+  const int m1  = std::max(pl.m1, 1);
+  const int wdt = 8 * ix.blocks * p.copies;
+  pl.qbuf  = alloc<float>(pl, p.device, int64_t{m1} * D, 0);
+  pl.qh    = alloc<__half>(pl, p.device, int64_t{m1} * p.ldu);
+  pl.qs    = alloc<float>(pl, p.device, int64_t{m1} * sw);
+  pl.Y     = alloc<__half>(pl, p.device, int64_t{m1} * wdt);
+  pl.codes = alloc<long long>(pl, p.device, int64_t{m1} * p.copies * L);
+  pl.seg   = alloc<int2>(pl, p.device, int64_t{m1} * p.copies);
+  pl.si    = alloc<long long>(pl, p.device, int64_t{m1} * pl.KO, 0xff);
+  pl.sd    = alloc<float>(pl, p.device, int64_t{m1} * pl.KO);
+  pl.bi    = alloc<long long>(pl, p.device, int64_t{m1} * k);
+  pl.bd    = alloc<float>(pl, p.device, int64_t{m1} * k);
+  if (sp.waves > 0) pl.done = alloc<int>(pl, p.device, int64_t{m1} * S * sp.waves, 0xff);
+  if (dbg.stats) pl.stats = alloc<long long>(pl, p.device, int64_t{m1} * 8, 0);
+  if (dbg.taps) {
+    pl.tap_cap  = p.copies * pl.lr;
+    pl.tap_cand = alloc<int>(pl, p.device, int64_t{m1} * pl.tap_cap, 0xff);
+    pl.tap_dist = alloc<float>(pl, p.device, int64_t{m1} * pl.tap_cap, 0);
+    pl.tap_n    = alloc<int>(pl, p.device, m1, 0);
+    pl.kept1_i  = alloc<long long>(pl, p.device, int64_t{m1} * pl.KO, 0xff);
+    pl.kept1_d  = alloc<float>(pl, p.device, int64_t{m1} * pl.KO, 0);
+  }
+
+  // first round: lists of this process's copies
+  auto& r1       = pl.r1;
+  r1.m           = pl.m1;
+  r1.nseg        = p.copies;
+  r1.seg         = pl.seg.as<int2>();
+  r1.lists       = p.lists.as<int>();
+  r1.stride      = p.stride;
+  r1.sketch      = p.sketch.as<signed char>();
+  r1.scale       = p.scale.as<float>();
+  r1.qs          = pl.qs.as<float>();
+  r1.sw          = sw;
+  r1.vectors     = p.vectors.as<__half>();
+  r1.D           = D;
+  r1.Q           = pl.qbuf.as<float>();
+  r1.R           = pl.R1;
+  r1.KO          = pl.KO;
+  r1.sketch_rank = sp.sketch_rank ? 1 : 0;
+  r1.fresh       = 1;
+  r1.si          = pl.si.as<long long>();
+  r1.sd          = pl.sd.as<float>();
+  r1.stats       = pl.stats.as<long long>();
+  if (dbg.taps) {
+    r1.tap_cand = pl.tap_cand.as<int>();
+    r1.tap_dist = pl.tap_dist.as<float>();
+    r1.tap_n    = pl.tap_n.as<int>();
+    r1.tap_cap  = pl.tap_cap;
+  }
+  size_round(pl, r1, p.copies * pl.lr, 0, p.device);
+  // waves: table rows of the start points
+  if (sp.waves > 0) {
+    auto& r2       = pl.r2;
+    r2             = kernels::round_args{};
+    r2.m           = pl.m1;
+    r2.nseg        = S;
+    r2.table       = p.table.as<int>();
+    r2.table_len   = ix.table_len;
+    r2.done        = pl.done.as<int>();
+    r2.done_stride = S * sp.waves;
+    r2.sketch      = r1.sketch;
+    r2.scale       = r1.scale;
+    r2.qs          = r1.qs;
+    r2.sw          = sw;
+    r2.vectors     = r1.vectors;
+    r2.D           = D;
+    r2.Q           = r1.Q;
+    r2.R           = pl.R2;
+    r2.KO          = pl.KO;
+    r2.sketch_rank = r1.sketch_rank;
+    r2.fresh       = 0;
+    r2.si          = r1.si;
+    r2.sd          = r1.sd;
+    r2.stats       = r1.stats;
+    size_round(pl, r2, S * ix.table_len, S * std::max(sp.waves - 1, 0), p.device);
+  }
+  kernels::round_allow_smem(pl.smem_max);
+
+  // one eager run (module loading), then the capture (search.cu:754-786)
+  OCTEX_CUDA_TRY(cudaDeviceSynchronize());
+  run_batch(ix, pl, p.stream, nullptr);
+  OCTEX_CUDA_TRY(cudaStreamSynchronize(p.stream));
+  cudaGraph_t graph = nullptr;
+  OCTEX_CUDA_TRY(cudaStreamBeginCapture(p.stream, cudaStreamCaptureModeThreadLocal));
+  try {
+    run_batch(ix, pl, p.stream, nullptr);
+  } catch (...) {
+    cudaStreamEndCapture(p.stream, &graph);
+    if (graph != nullptr) cudaGraphDestroy(graph);
+    throw;
+  }
+  OCTEX_CUDA_TRY(cudaStreamEndCapture(p.stream, &graph));
+  OCTEX_CUDA_TRY(cudaGraphInstantiate(&pl.graph, graph, 0));
+  OCTEX_CUDA_TRY(cudaGraphDestroy(graph));
+  OCTEX_CUDA_TRY(cudaEventCreateWithFlags(&pl.done_ev, cudaEventDisableTiming));
+  return plp;
+}
+
+auto get_plan(index_impl& ix, search_params const& sp, int m, int k) -> std::shared_ptr<plan>
+{
+  const debug_options dbg = ix_debug(ix);
+  std::string key = std::to_string(m) + "/" + std::to_string(k) + "/" + std::to_string(sp.read) +
+                    "/" + std::to_string(sp.starts) + "/" + std::to_string(sp.waves) + "/" +
+                    std::to_string(sp.rerank) + "/" + std::to_string(sp.wave_rerank) + "/" +
+                    std::to_string(sp.sketch_rank) + "/" + std::to_string(sp.final_rerank) + "/" +
+                    std::to_string(dbg.stats) + std::to_string(dbg.taps);
+  std::lock_guard<std::mutex> lock(ix.mu);
+  auto it = ix.plans.find(key);
+  if (it != ix.plans.end()) return it->second;
+  // one cached configuration: the previous buffers and graph go before the new ones come
+  // (search.cu:807-812)
+  ix.plans.clear();
+  auto pl       = make_plan(ix, sp, m, k, dbg);
+  ix.plans[key] = pl;
+  return pl;
+}
+
+void search_impl(resources const& res,
+                 search_params const& sp,
+                 index const& idx,
+                 const float* queries,
+                 int64_t nq,
+                 int64_t qdim,
+                 int64_t* neighbors,
+                 float* distances,
+                 int64_t k,
+                 bool host_out,
+                 bool resident)
+{
+  auto& ix = idx.impl();
+  OCTEX_EXPECTS(qdim == ix.dim, "octex: query dimension differs from the index");
+  OCTEX_EXPECTS(k >= 1, "octex: k >= 1");
+  if (nq == 0) return;
+  int cur = 0;
+  OCTEX_CUDA_TRY(cudaGetDevice(&cur));
+  cudaStream_t caller = res.stream;
+  const int m         = static_cast<int>(std::min<int64_t>(std::max(sp.batch, 1), nq));
+  auto pl             = get_plan(ix, sp, m, static_cast<int>(k));
+  std::lock_guard<std::mutex> lock(pl->mu);
+  const int D    = static_cast<int>(ix.dim);
+  auto& p        = ix.part;
+  cudaStream_t s = p.stream;
+
+  // the work of this call starts after what the caller queued on its stream (search.cu:841-848)
+  cudaEvent_t start = nullptr;
+  OCTEX_CUDA_TRY(cudaEventCreateWithFlags(&start, cudaEventDisableTiming));
+  OCTEX_CUDA_TRY(cudaEventRecord(start, caller));
+  OCTEX_CUDA_TRY(cudaSetDevice(p.device));
+  OCTEX_CUDA_TRY(cudaStreamWaitEvent(s, start, 0));
+  for (int64_t b0 = 0; b0 < nq; b0 += m) {
+    const int n = static_cast<int>(std::min<int64_t>(m, nq - b0));
+    if (!resident) {
+      OCTEX_CUDA_TRY(cudaMemcpyAsync(pl->qbuf.ptr, queries + b0 * D, sizeof(float) * n * D,
+                                     cudaMemcpyDefault, s));
+      if (n < pl->m1) kernels::pad_rows(pl->qbuf.as<float>(), n, pl->m1, D, s);  // search.cu:870-883
+    }
+    OCTEX_CUDA_TRY(cudaGraphLaunch(pl->graph, s));
+    if (!resident) {
+      OCTEX_CUDA_TRY(cudaMemcpyAsync(neighbors + b0 * k, pl->bi.ptr, sizeof(int64_t) * n * k,
+                                     cudaMemcpyDefault, s));
+      OCTEX_CUDA_TRY(cudaMemcpyAsync(distances + b0 * k, pl->bd.ptr, sizeof(float) * n * k,
+                                     cudaMemcpyDefault, s));
+    }
+  }
+  OCTEX_CUDA_TRY(cudaEventRecord(pl->done_ev, s));
+  OCTEX_CUDA_TRY(cudaSetDevice(cur));
+  OCTEX_CUDA_TRY(cudaStreamWaitEvent(caller, pl->done_ev, 0));
+  if (host_out) OCTEX_CUDA_TRY(cudaStreamSynchronize(caller));
+  OCTEX_CUDA_TRY(cudaEventDestroy(start));
+}
+
+}  // namespace detail
+
+void search(resources const& res, search_params const& params, index const& idx,
+            host_matrix_view<const float> queries, host_matrix_view<int64_t> neighbors,
+            host_matrix_view<float> distances)
+{
+  OCTEX_EXPECTS(neighbors.rows == queries.rows && distances.rows == queries.rows &&
+                  distances.cols == neighbors.cols,
+                "octex: output shapes");
+  detail::search_impl(res, params, idx, queries.data, queries.rows, queries.cols, neighbors.data,
+                      distances.data, neighbors.cols, true, false);
+}
+
+void search(resources const& res, search_params const& params, index const& idx,
+            device_matrix_view<const float> queries, device_matrix_view<int64_t> neighbors,
+            device_matrix_view<float> distances)
+{
+  OCTEX_EXPECTS(neighbors.rows == queries.rows && distances.rows == queries.rows &&
+                  distances.cols == neighbors.cols,
+                "octex: output shapes");
+  detail::search_impl(res, params, idx, queries.data, queries.rows, queries.cols, neighbors.data,
+                      distances.data, neighbors.cols, false, false);
+}
+
+}  // namespace octex_b200

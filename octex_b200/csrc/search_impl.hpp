@@ -1,0 +1,54 @@
+// Buffers and graph of one batch shape and one set of search parameters (the reference's
+// plan / gpu_plan, cpp/src/neighbors/octex/search.cu:35-80 of hpdic/octex, for one GPU).
+#pragma once
+
+#include "index_impl.hpp"
+#include "kernels.hpp"
+
+#include <mutex>
+#include <vector>
+
+namespace octex_b200::detail {
+
+struct plan {
+  search_params sp;
+  debug_options dbg;
+  int device = 0;
+  int m = 0, k = 0, KO = 0, lr = 0, R1 = 0, R2 = 0, FR = 0;
+  int m1 = 0;  // queries of a batch handled by this process
+  dbuf qbuf, qh, qs, Y, codes, seg, si, sd, done, bi, bd, stats;
+  dbuf tap_cand, tap_dist, tap_n, kept1_i, kept1_d;
+  int tap_cap = 0;
+  std::vector<dbuf> scratch_cand, scratch_dist;
+  kernels::round_args r1, r2;
+  size_t smem_max       = 0;
+  cudaGraphExec_t graph = nullptr;
+  cudaEvent_t done_ev   = nullptr;
+  int64_t buffer_bytes  = 0;
+  std::mutex mu;  // one search at a time per plan
+  ~plan();
+};
+
+inline auto ix_debug(index_impl const& ix) -> debug_options { return ix.debug; }
+
+void search_impl(resources const& res,
+                 search_params const& sp,
+                 index const& idx,
+                 const float* queries,
+                 int64_t nq,
+                 int64_t qdim,
+                 int64_t* neighbors,
+                 float* distances,
+                 int64_t k,
+                 bool host_out,
+                 bool resident);
+
+/// One batch of the queries already on the GPU, launched kernel by kernel with an event between
+/// them: milliseconds of center+sketch, projection, cell codes, lookup, first round, each wave,
+/// best k (the per-kernel counterpart of detail::timed_batch, search.cu:965-981 of the reference).
+auto profile_batch(resources const& res, search_params const& sp, index const& idx, int64_t nq,
+                   int64_t k) -> std::vector<float>;
+
+auto get_plan(index_impl& ix, search_params const& sp, int m, int k) -> std::shared_ptr<plan>;
+
+}  // namespace octex_b200::detail

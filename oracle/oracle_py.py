@@ -67,6 +67,23 @@ def ref_e8(fma: bool = False):
     return C.CDLL(p) if os.path.exists(p) else None
 
 
+def ref_e8_cuda():
+    """The reference's E8 decode compiled as device code (needs a GPU), or None when not built."""
+    p = os.path.join(_HERE, "_ref", "libe8_ref_cuda.so")
+    return C.CDLL(p) if os.path.exists(p) else None
+
+
+def ref_cuda_cell_code(y: np.ndarray, blocks: int, inv_f: float) -> np.ndarray:
+    lib_ = ref_e8_cuda()
+    y = np.ascontiguousarray(y, np.float32)
+    h = np.zeros(y.shape[0], np.int64)
+    rc = lib_.ref_cuda_cell_code(_ptr(y), C.c_int64(y.shape[0]), C.c_int32(blocks),
+                                 C.c_float(inv_f), _ptr(h))
+    if rc != 0:
+        raise RuntimeError(f"CUDA error {rc} in the reference E8 kernel")
+    return h
+
+
 def _ptr(a):
     return None if a is None else a.ctypes.data_as(C.c_void_p)
 

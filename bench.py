@@ -46,13 +46,12 @@ WORKLOADS = {
                    sketch_width=64, table_len=32)),
 }
 LADDER = [
-    dict(read=8, starts=32, waves=1, rerank=64, wave_rerank=64),
-    dict(read=8, starts=32, waves=1, rerank=128, wave_rerank=128),
-    dict(read=8, starts=32, waves=2, rerank=128, wave_rerank=128),
-    dict(read=16, starts=64, waves=1, rerank=128, wave_rerank=128),
-    dict(read=16, starts=64, waves=2, rerank=128, wave_rerank=128),
-    dict(read=32, starts=128, waves=2, rerank=128, wave_rerank=128),
+    dict(read=8, starts=32, waves=1, rerank=256, wave_rerank=256),
+    dict(read=8, starts=32, waves=2, rerank=256, wave_rerank=256),
+    dict(read=32, starts=32, waves=2, rerank=256, wave_rerank=256),
+    dict(read=32, starts=32, waves=3, rerank=256, wave_rerank=256),
     dict(read=32, starts=128, waves=3, rerank=256, wave_rerank=256),
+    dict(read=32, starts=128, waves=2, rerank=512, wave_rerank=512),
     dict(read=32, starts=256, waves=4, rerank=512, wave_rerank=512),
 ]
 
@@ -160,7 +159,7 @@ def run_reference(args, rank, world):
     dev = "cuda" if torch.cuda.is_available() else "cpu"
     arrays, meta = build_index.build_arrays(base, build_index.IndexParams(**w["build"]), device=dev)
     ox = oracle_py.Index(arrays, meta)
-    sp = dict(LADDER[args.ladder_start])
+    sp = json.loads(args.search) if args.search else dict(LADDER[args.ladder_start])
     sample = queries[:args.cpu_sample]
     cores = os.cpu_count() or 1
     for _ in range(max(args.warmup, 1)):
@@ -195,6 +194,7 @@ def main():
     ap.add_argument("--ladder-start", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--copies", type=int, default=0, help="override the copies of the build")
+    ap.add_argument("--search", default="", help="JSON search parameters (skips the ladder)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
@@ -233,7 +233,7 @@ def main():
 
     # search parameters: the cheapest rung of the ladder that reaches recall@10 >= 0.99
     chosen, rec = None, 0.0
-    for sp in LADDER[args.ladder_start:]:
+    for sp in ([json.loads(args.search)] if args.search else LADDER[args.ladder_start:]):
         _, ids = idx.search(q_dev, K, **sp)
         r = recall_of(ids.cpu().numpy(), truth)
         log(f"[rank {rank}] {sp} recall@10 {r:.4f}")

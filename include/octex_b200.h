@@ -129,7 +129,7 @@ struct cuvsOctexSearchParams {
   int32_t final_rerank;
   bool balanced_gather; /* accepted, ignored: one implementation */
   bool fused_merge;     /* accepted, ignored */
-  bool use_graph;       /* accepted, ignored */
+  bool use_graph;       /* false: direct kernel launches instead of replaying the batch graph */
 };
 typedef struct cuvsOctexSearchParams* cuvsOctexSearchParams_t;
 /* octex.h:189-192 */

@@ -42,10 +42,11 @@ struct search_params {
   int batch            = 10000; ///< queries per captured batch
   bool sketch_rank     = false; ///< rank by the sketch, rerank exactly only at the end
   int final_rerank     = 32;    ///< sketch-rank mode: kept entries reranked exactly at the end
-  /// Ablation switches of the reference. This library has one implementation of each step (the
-  /// balanced gather, the fused merge, one graph per batch); the fields are accepted and ignored.
+  /// Ablation switches of the reference. This library has one implementation of the gather and of
+  /// the merge; those two fields are accepted and ignored.
   bool balanced_gather = true;
   bool fused_merge     = true;
+  /// false: direct kernel launches for every batch instead of replaying its CUDA graph.
   bool use_graph       = true;
 };
 

@@ -19,7 +19,7 @@ library.
 """
 from __future__ import annotations
 
-import math
+import sys
 from dataclasses import dataclass, field
 
 import numpy as np
@@ -297,7 +297,7 @@ def build_arrays(dataset, params: IndexParams, device: str | torch.device = "cpu
                                for r0 in range(0, n, 1 << 18)]) + sh
             per_copy.append(_copy_cells(y, params))
             if verbose and (c % 10 == 0 or c == params.copies - 1):
-                print(f"  copy {c}: cells per level {per_copy[-1][4]}", flush=True)
+                print(f"  copy {c}: cells per level {per_copy[-1][4]}", file=sys.stderr, flush=True)
         del xc
         rows = [sum(pc[4]) for pc in per_copy]
         Lmax = max(rows) * params.list_len

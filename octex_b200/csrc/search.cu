@@ -376,7 +376,10 @@ void search_impl(resources const& res,
                                      cudaMemcpyDefault, s));
       if (n < pl->m1) kernels::pad_rows(pl->qbuf.as<float>(), n, pl->m1, D, s);  // search.cu:870-883
     }
-    OCTEX_CUDA_TRY(cudaGraphLaunch(pl->graph, s));
+    if (sp.use_graph)
+      OCTEX_CUDA_TRY(cudaGraphLaunch(pl->graph, s));
+    else
+      run_batch(ix, *pl, s, nullptr);  // search_params::use_graph = false: direct launches
     if (!resident) {
       OCTEX_CUDA_TRY(cudaMemcpyAsync(neighbors + b0 * k, pl->bi.ptr, sizeof(int64_t) * n * k,
                                      cudaMemcpyDefault, s));

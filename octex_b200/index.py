@@ -19,6 +19,7 @@ from . import _lib
 METRICS = ("sqeuclidean", "l2")
 SEARCH_PARAMS = ("read", "starts", "waves", "rerank", "wave_rerank", "batch", "sketch_rank",
                  "final_rerank")
+_SWITCHES = ("use_graph",)  # fields of the C struct the reference's Python layer does not expose
 LOAD_PARAMS = ("devices", "placement", "vectors_on_host", "shard_vectors", "table_on_host",
                "sketch", "parts", "copies_per_part", "copies_limit", "list_limit")
 PLACEMENTS = ("shard", "replicate")
@@ -66,7 +67,7 @@ class _Resources:
 def search_params(**kw) -> _lib.SearchParams:
     """struct cuvsOctexSearchParams with the defaults of the C++ API, then ``kw``."""
     for name in kw:
-        if name not in SEARCH_PARAMS:
+        if name not in SEARCH_PARAMS and name not in _SWITCHES:
             raise TypeError(f"octex: unknown search parameter {name!r}; valid: {', '.join(SEARCH_PARAMS)}")
     pp = C.POINTER(_lib.SearchParams)()
     _lib.check(_lib.lib().cuvsOctexSearchParamsCreate(C.byref(pp)))
@@ -75,7 +76,7 @@ def search_params(**kw) -> _lib.SearchParams:
     _lib.check(_lib.lib().cuvsOctexSearchParamsDestroy(pp))
     for name, value in kw.items():
         if value is not None:
-            setattr(p, name, bool(value) if name == "sketch_rank" else int(value))
+            setattr(p, name, bool(value) if name in ("sketch_rank",) + _SWITCHES else int(value))
     return p
 
 

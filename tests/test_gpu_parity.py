@@ -298,7 +298,7 @@ def test_full_size_properties():
                                      log_buckets=16, table_len=32)
     arrays, meta = build_index.build_arrays(base, params, device="cuda", keep_on_device=True)
     idx = octex_b200.attach(arrays, meta, borrow=True)
-    dist, ids = idx.search(queries, 10, read=8, starts=32, waves=1)
+    dist, ids = idx.search(queries, 10, read=32, starts=128, waves=3, rerank=256, wave_rerank=256)
     assert (np.diff(dist, axis=1) >= 0).all()
     assert ids.min() >= 0 and ids.max() < meta["n"]
     assert all(len(set(r.tolist())) == 10 for r in ids)
@@ -309,6 +309,6 @@ def test_full_size_properties():
     d_all = (q * q).sum(1)[:, None] - 2 * q @ v.T + (v * v).sum(1)[None, :]
     truth = d_all.topk(10, dim=1, largest=False).indices.cpu().numpy()
     r = recall(ids, truth)
-    print(f"recall@10 {r:.4f} (read 8, starts 32, waves 1, 24 copies)")
+    print(f"recall@10 {r:.4f} (read 32, starts 128, waves 3, rerank 256, 24 copies)")
     assert r >= 0.95
     idx.close()

@@ -132,13 +132,13 @@ def algorithmic_bytes(stats, sp, meta, k):
     D, S, L2 = meta["dim"], meta["sketch_width"], meta.get("table_len", 0)
     KO = max(sp["starts"], k)
     n1 = stats[:, 3]
-    r1 = np.minimum(n1, sp["rerank"])
+    r1 = np.minimum(n1, sp["rerank"])  # the first round starts from an empty kept list
     waves = sp["waves"]
     lists = (4 * stats[:, 2] + n1 * S + r1 * 2 * D + 4 * D + 4 * S + KO * 12).sum()
     out = {"probe": int((stats[:, 0] * 16 + stats[:, 1] * 8).sum()),
            "round_lists": int(lists)}
     if waves:
-        rerank_w = stats[:, 6] - r1
+        rerank_w = stats[:, 7] - r1  # rows the waves read (ids already kept are not read again)
         rows = (stats[:, 4] * 4 * L2 + stats[:, 5] * S + rerank_w * 2 * D).sum() \
             + waves * len(stats) * (4 * D + 4 * S + 2 * KO * 12)
         out["round_rows"] = int(rows / waves)  # per launch

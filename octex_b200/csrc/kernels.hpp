@@ -54,6 +54,7 @@ struct round_args {
   const int2* seg = nullptr;
   const int* lists = nullptr;
   int64_t stride = 0;
+  int lr = 0;  // entries read per non-empty segment (every segment is 0 or lr long)
   // rows mode: the first `starts` kept entries no earlier wave expanded; their table rows
   const int* table = nullptr;
   int table_len = 0;
@@ -80,7 +81,7 @@ struct round_args {
   int ht_slots = 0;   // ints of the hash set region (>= largest set used, >= pick_slots)
   int log_cap = 0;    // log2 of the largest gather hash set
   int nmax = 0;       // capacity of the candidate / distance arrays
-  int P = 0;          // keys sorted by the merge (power of two >= KO + selected)
+  int P = 0;          // keys sorted by the merge (power of two >= KO)
   int* cand_global = nullptr;    // [m, nmax] when the candidates do not fit shared memory
   float* dist_global = nullptr;  // [m, nmax]
   // observation (all may be null)
@@ -90,7 +91,8 @@ struct round_args {
   int tap_cap = 0;
   long long* stats = nullptr;  // [m, 8]: [2] entries read, [3] distinct ids first round,
                                // [4] table rows expanded, [5] distinct ids of waves,
-                               // [6] rows reranked exactly
+                               // [6] rows selected for the exact rerank, [7] of them read
+                               // (a selected id already in the kept list is not read again)
 };
 size_t round_smem_bytes(const round_args& a);
 void round_lists(const round_args& a, cudaStream_t s);

@@ -1,0 +1,330 @@
+// Preparation kernels of a batch (sm_100a): padding, centring, projection, cell codes, cell lookup, best k.
+//
+// Semantics follow the reference's kernels (hpdic/octex,
+// cpp/src/neighbors/octex/detail/search_kernels.cuh); each kernel cites the lines it answers.
+// The organisation is different: the cell codes of all levels are produced where the projected
+// coordinates are produced, and each round (gather, dedup, sketch scoring, selection, exact
+// rerank, merge into the kept list, and for waves the choice of start points) is one kernel that
+// keeps a query's candidates in shared memory from the first list entry to the kept list.
+
+#include "kernels.hpp"
+
+#include "e8.cuh"
+
+#include <cfloat>
+#include <cmath>
+
+namespace octex_b200::kernels {
+
+namespace {
+
+inline unsigned blocks_for(int64_t total, int threads)
+{
+  return static_cast<unsigned>((total + threads - 1) / threads);
+}
+
+// ---- padding, centring, sketch-space query -------------------------------------------------
+
+// search_kernels.cuh:72-78
+__global__ void pad_rows_kernel(float* __restrict__ q, int from, int m, int D)
+{
+  const int64_t t     = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t total = static_cast<int64_t>(m - from) * D;
+  if (t >= total) return;
+  q[static_cast<int64_t>(from) * D + t] = q[t % D];
+}
+
+// Centre (search_kernels.cuh:57-69) fused with the sketch-space projection of the query
+// (search.cu:321-341): one block per query, the centred query in shared memory, thread s owns
+// sketch coordinate s.
+__global__ void center_sketch_kernel(const float* __restrict__ q,
+                                     const float* __restrict__ mean,
+                                     const float* __restrict__ basis,
+                                     int D,
+                                     int S,
+                                     __half* __restrict__ qh,
+                                     int ldq,
+                                     float* __restrict__ qs)
+{
+  extern __shared__ float qc[];
+  const int row = blockIdx.x;
+  for (int d = threadIdx.x; d < ldq; d += blockDim.x) {
+    float v = 0.f;
+    if (d < D) {
+      v     = __fsub_rn(q[static_cast<int64_t>(row) * D + d], mean[d]);
+      qc[d] = v;
+    }
+    qh[static_cast<int64_t>(row) * ldq + d] = __float2half_rn(v);
+  }
+  __syncthreads();
+  for (int s = threadIdx.x; s < S; s += blockDim.x) {
+    float acc = 0.f;
+    for (int d = 0; d < D; d++)
+      acc = __fmaf_rn(qc[d], basis[static_cast<int64_t>(d) * S + s], acc);
+    qs[static_cast<int64_t>(row) * S + s] = acc;
+  }
+}
+
+// ---- projection in the checker's summation order ---------------------------------------------
+
+// Y = half(fp32(qh . ut^T) + shift), search.cu:303-320. 64 x 64 output tile per block, 16 x 16
+// threads with 4 x 4 outputs each; every output accumulates its dot product with one fused
+// multiply-add per dimension in dimension order, which is the order the CPU checker uses, so the
+// result is comparable bit for bit. The tensor-core projection of the search path is checked
+// against this one.
+constexpr int kOrdTile = 64, kOrdK = 32;
+__global__ void __launch_bounds__(256) project_ordered_kernel(const __half* __restrict__ qh,
+                                                              int ldq,
+                                                              const __half* __restrict__ ut,
+                                                              int ldu,
+                                                              const __half* __restrict__ shift,
+                                                              int m,
+                                                              int N,
+                                                              int D,
+                                                              __half* __restrict__ Y)
+{
+  __shared__ float sa[kOrdK][kOrdTile + 1];
+  __shared__ float sb[kOrdK][kOrdTile + 1];
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const int row0 = blockIdx.y * kOrdTile, col0 = blockIdx.x * kOrdTile;
+  float acc[4][4] = {};
+  for (int k0 = 0; k0 < D; k0 += kOrdK) {
+    for (int i = threadIdx.x; i < kOrdTile * kOrdK; i += 256) {
+      const int r = i / kOrdK, k = i % kOrdK;
+      float a = 0.f, b = 0.f;
+      if (k0 + k < D) {
+        if (row0 + r < m) a = __half2float(qh[static_cast<int64_t>(row0 + r) * ldq + k0 + k]);
+        if (col0 + r < N) b = __half2float(ut[static_cast<int64_t>(col0 + r) * ldu + k0 + k]);
+      }
+      sa[k][r] = a;
+      sb[k][r] = b;
+    }
+    __syncthreads();
+    const int kk = min(kOrdK, D - k0);
+    for (int k = 0; k < kk; k++) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        a[i] = sa[k][ty * 4 + i];
+        b[i] = sb[k][tx * 4 + i];
+      }
+#pragma unroll
+      for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+          acc[i][j] = __fmaf_rn(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const int r = row0 + ty * 4 + i;
+    if (r >= m) continue;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const int c = col0 + tx * 4 + j;
+      if (c < N)
+        Y[static_cast<int64_t>(r) * N + c] =
+          __float2half_rn(__fadd_rn(acc[i][j], __half2float(shift[c])));
+    }
+  }
+}
+
+// ---- cell codes of all levels from projected coordinates -----------------------------------
+
+template <int B>
+__global__ void decode_codes_kernel(const __half* __restrict__ Y,
+                                    int64_t pairs,
+                                    int C,
+                                    int L,
+                                    const float* __restrict__ inv_f,
+                                    const unsigned char* __restrict__ level_on,
+                                    long long* __restrict__ codes)
+{
+  const int64_t t = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (t >= pairs) return;
+  const int c = static_cast<int>(t % C);
+  float y[8 * B];
+  const uint4* yp = reinterpret_cast<const uint4*>(Y + t * 8 * B);
+#pragma unroll
+  for (int i = 0; i < B; i++) {
+    const uint4 v     = yp[i];
+    const __half2* h2 = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const float2 f   = __half22float2(h2[j]);
+      y[8 * i + 2 * j] = f.x;
+      y[8 * i + 2 * j + 1] = f.y;
+    }
+  }
+  for (int j = 0; j < L; j++) {
+    long long h = 0;
+    if (level_on == nullptr || level_on[c * L + j]) h = cell_code<B>(y, inv_f[j]);
+    codes[t * L + j] = h;
+  }
+}
+
+// Cell code of rows of 8 * B float32 coordinates at one scale (the device function on its own,
+// for checks against other implementations of the decode).
+template <int B>
+__global__ void cell_codes_f32_kernel(const float* __restrict__ y, int64_t n, float inv_f,
+                                      long long* __restrict__ codes)
+{
+  const int64_t t = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (t >= n) return;
+  float v[8 * B];
+#pragma unroll
+  for (int i = 0; i < 8 * B; i++)
+    v[i] = y[t * 8 * B + i];
+  codes[t] = cell_code<B>(v, inv_f);
+}
+
+// ---- cell lookup -----------------------------------------------------------------------------
+
+// search_kernels.cuh:100-126: the finest level whose cell holds a list. One thread per
+// (query, copy); the codes of all levels are already there, so a level costs two dependent
+// reads (bucket bounds, then the short key scan) and no arithmetic.
+__global__ void probe_kernel(const long long* __restrict__ codes,
+                             int64_t pairs,
+                             int C,
+                             int L,
+                             const int* __restrict__ offsets,
+                             int64_t T1,
+                             const long long* __restrict__ keys,
+                             int64_t mmax,
+                             const int* __restrict__ base,
+                             const unsigned char* __restrict__ level_on,
+                             int list_len,
+                             int lr,
+                             int log_buckets,
+                             int2* __restrict__ seg,
+                             long long* __restrict__ stats)
+{
+  const int64_t t = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (t >= pairs) return;
+  const int c             = static_cast<int>(t % C);
+  const long long bmask   = (1LL << log_buckets) - 1;
+  int2 sg                 = make_int2(0, 0);
+  long long tried = 0, scanned = 0;
+  for (int j = 0; j < L; j++) {
+    if (level_on != nullptr && !level_on[c * L + j]) continue;
+    const long long h   = codes[t * L + j];
+    const int64_t cl    = static_cast<int64_t>(c) * L + j;
+    const int* o        = offsets + cl * T1 + static_cast<int>(h & bmask);
+    const int lo = o[0], hi = o[1];
+    const long long* kk = keys + cl * mmax;
+    tried++;
+    bool found = false;
+    for (int p = lo; p < hi; p++) {
+      scanned++;
+      if (kk[p] == h) {
+        sg    = make_int2((base[cl] + p) * list_len, lr);
+        found = true;
+        break;
+      }
+    }
+    if (found) break;
+  }
+  seg[t] = sg;
+  if (stats != nullptr) {
+    const int64_t q = t / C;
+    atomicAdd(reinterpret_cast<unsigned long long*>(stats + q * 8), static_cast<unsigned long long>(tried));
+    atomicAdd(reinterpret_cast<unsigned long long*>(stats + q * 8 + 1), static_cast<unsigned long long>(scanned));
+  }
+}
+
+// search_kernels.cuh:672-685
+__global__ void take_k_kernel(const long long* __restrict__ si,
+                              const float* __restrict__ sd,
+                              int KO,
+                              int k,
+                              int m,
+                              long long* __restrict__ bi,
+                              float* __restrict__ bd)
+{
+  const int64_t t = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (t >= static_cast<int64_t>(m) * k) return;
+  const int64_t q = t / k, j = t % k;
+  bi[t] = si[q * KO + j];
+  bd[t] = sd[q * KO + j];
+}
+
+
+}  // namespace
+
+// ---- launchers ---------------------------------------------------------------------------------
+
+void pad_rows(float* q, int from, int m, int D, cudaStream_t s)
+{
+  if (from >= m) return;
+  pad_rows_kernel<<<blocks_for(static_cast<int64_t>(m - from) * D, 256), 256, 0, s>>>(q, from, m, D);
+}
+
+void center_sketch(const float* q, const float* mean, const float* basis, int m, int D, int S,
+                   __half* qh, int ldq, float* qs, cudaStream_t s)
+{
+  if (m <= 0) return;
+  center_sketch_kernel<<<m, 128, sizeof(float) * D, s>>>(q, mean, basis, D, S, qh, ldq, qs);
+}
+
+void project_ordered(const __half* qh, int ldq, const __half* ut, int ldu, const __half* shift,
+                     int m, int N, int D, __half* Y, cudaStream_t s)
+{
+  if (m <= 0 || N <= 0) return;
+  dim3 grid((N + kOrdTile - 1) / kOrdTile, (m + kOrdTile - 1) / kOrdTile);
+  project_ordered_kernel<<<grid, 256, 0, s>>>(qh, ldq, ut, ldu, shift, m, N, D, Y);
+}
+
+void decode_codes(const __half* Y, int64_t pairs, int C, int blocks, int L, const float* inv_f,
+                  const unsigned char* level_on, long long* codes, cudaStream_t s)
+{
+  if (pairs <= 0) return;
+  const unsigned g = blocks_for(pairs, 128);
+  switch (blocks) {
+    case 1: decode_codes_kernel<1><<<g, 128, 0, s>>>(Y, pairs, C, L, inv_f, level_on, codes); break;
+    case 2: decode_codes_kernel<2><<<g, 128, 0, s>>>(Y, pairs, C, L, inv_f, level_on, codes); break;
+    case 3: decode_codes_kernel<3><<<g, 128, 0, s>>>(Y, pairs, C, L, inv_f, level_on, codes); break;
+    case 4: decode_codes_kernel<4><<<g, 128, 0, s>>>(Y, pairs, C, L, inv_f, level_on, codes); break;
+    case 5: decode_codes_kernel<5><<<g, 128, 0, s>>>(Y, pairs, C, L, inv_f, level_on, codes); break;
+    case 6: decode_codes_kernel<6><<<g, 128, 0, s>>>(Y, pairs, C, L, inv_f, level_on, codes); break;
+    case 8: decode_codes_kernel<8><<<g, 128, 0, s>>>(Y, pairs, C, L, inv_f, level_on, codes); break;
+    default: break;  // the loader rejects other block counts
+  }
+}
+
+void cell_codes_f32(const float* y, int64_t n, int blocks, float inv_f, long long* codes,
+                    cudaStream_t s)
+{
+  if (n <= 0) return;
+  const unsigned g = blocks_for(n, 128);
+  switch (blocks) {
+    case 1: cell_codes_f32_kernel<1><<<g, 128, 0, s>>>(y, n, inv_f, codes); break;
+    case 2: cell_codes_f32_kernel<2><<<g, 128, 0, s>>>(y, n, inv_f, codes); break;
+    case 3: cell_codes_f32_kernel<3><<<g, 128, 0, s>>>(y, n, inv_f, codes); break;
+    case 4: cell_codes_f32_kernel<4><<<g, 128, 0, s>>>(y, n, inv_f, codes); break;
+    case 5: cell_codes_f32_kernel<5><<<g, 128, 0, s>>>(y, n, inv_f, codes); break;
+    case 6: cell_codes_f32_kernel<6><<<g, 128, 0, s>>>(y, n, inv_f, codes); break;
+    case 8: cell_codes_f32_kernel<8><<<g, 128, 0, s>>>(y, n, inv_f, codes); break;
+    default: break;
+  }
+}
+
+void probe(const long long* codes, int m, int C, int L, const int* offsets, int64_t T1,
+           const long long* keys, int64_t mmax, const int* base, const unsigned char* level_on,
+           int list_len, int lr, int log_buckets, int2* seg, long long* stats, cudaStream_t s)
+{
+  const int64_t pairs = static_cast<int64_t>(m) * C;
+  if (pairs <= 0) return;
+  probe_kernel<<<blocks_for(pairs, 256), 256, 0, s>>>(codes, pairs, C, L, offsets, T1, keys, mmax,
+                                                      base, level_on, list_len, lr, log_buckets,
+                                                      seg, stats);
+}
+
+void take_k(const long long* si, const float* sd, int KO, int k, int m, long long* bi, float* bd,
+            cudaStream_t s)
+{
+  if (m <= 0) return;
+  take_k_kernel<<<blocks_for(static_cast<int64_t>(m) * k, 256), 256, 0, s>>>(si, sd, KO, k, m, bi, bd);
+}
+
+}  // namespace octex_b200::kernels

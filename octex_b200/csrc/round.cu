@@ -1,0 +1,826 @@
+// One round of the search per query block (sm_100a): gather, dedup, sketch scoring, selection,
+// exact rerank and merge into the kept list in one kernel; for waves the choice of the start points
+// comes first in the same kernel. A query's candidates stay in shared memory from the first list
+// entry to the kept list.
+//
+// Semantics follow the reference's per-step kernels (hpdic/octex,
+// cpp/src/neighbors/octex/detail/search_kernels.cuh): gather_kernel :138-253, select_smallest
+// :259-322, exact_distances :325-342, load_keys / bitonic_sort / store_keys :345-415,
+// rerank_keep_kernel :421-467, sketch_keep_kernel :471-508, merge_kept_kernel :517-564,
+// pick_starts_kernel :571-631, final_rerank_kernel :634-669. What differs is how the work is laid
+// out: the kept list is never fully re-sorted (the best KO keys are selected by radix passes and
+// only those are sorted), candidates already in the kept list are not reranked again (their key is
+// already there), and every thread keeps several independent loads in flight.
+
+#include "kernels.hpp"
+
+#include <cfloat>
+#include <cmath>
+
+namespace octex_b200::kernels {
+
+namespace {
+
+constexpr unsigned kIdHash          = 2654435761u;
+constexpr unsigned long long kNoKey = ~0ULL;
+
+/// Offsets (in 4-byte words) of the regions of a round block's shared memory.
+struct round_layout {
+  int table, cand, dist, pool, sorted, sid, sdv, qv, sc, fq, st, len, hist, wsum, ctrl, kid, kd, words;
+  __host__ __device__ explicit round_layout(const round_args& a)
+  {
+    const int in_smem = a.cand_global == nullptr ? a.nmax : 0;
+    const int rm      = a.sketch_rank ? a.KO : a.R;
+    int at            = 0;
+    auto take         = [&](int n) {
+      int o = at;
+      at += (n + 3) & ~3;  // keep every region 16-byte aligned
+      return o;
+    };
+    table  = take(a.ht_slots);
+    cand   = take(in_smem);
+    dist   = take(in_smem);
+    pool   = take(2 * (a.KO + rm));
+    sorted = take(2 * a.P);
+    sid    = take(rm);
+    sdv    = take(rm);
+    qv     = take(a.sw);
+    sc     = take(a.sw);
+    fq     = take(a.D);
+    st     = take(a.nseg);
+    len    = take(a.nseg);
+    hist   = take(256);
+    wsum   = take(16);
+    ctrl   = take(8);
+    kid    = take(a.KO);
+    kd     = take(a.KO);
+    words  = at;
+  }
+};
+
+__device__ __forceinline__ int hash_log_of(int total, int log_cap)
+{
+  // smallest e in [kMinLogHash, log_cap] with 2^e >= 1.5 * total (search_kernels.cuh:33-38)
+  const int need = (3 * total + 1) / 2;
+  int e          = kMinLogHash;
+  while (e < log_cap && (1 << e) < need)
+    e++;
+  return e;
+}
+
+/// Exclusive prefix of v over the block (kRoundThreads threads); total = the sum.
+__device__ __forceinline__ int block_scan(int v, int* wsum, int& total)
+{
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  constexpr int nw = kRoundThreads / 32;
+  int inc          = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int u = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += u;
+  }
+  if (lane == 31) wsum[warp] = inc;
+  __syncthreads();
+  if (warp == 0) {
+    const int w = lane < nw ? wsum[lane] : 0;
+    int winc    = w;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int u = __shfl_up_sync(0xffffffffu, winc, o);
+      if (lane >= o) winc += u;
+    }
+    if (lane < nw) wsum[lane] = winc - w;
+    if (lane == nw - 1) wsum[nw] = winc;
+  }
+  __syncthreads();
+  const int out = wsum[warp] + inc - v;
+  total         = wsum[nw];
+  __syncthreads();
+  return out;
+}
+
+/// (distance bits << 32) | id: the total order of every kept list (search_kernels.cuh:365-368).
+__device__ __forceinline__ unsigned long long rank_key(float d, unsigned id)
+{
+  return (static_cast<unsigned long long>(__float_as_uint(d)) << 32) | id;
+}
+
+/// Ascending bitonic sort of P (power of two) 64-bit keys in shared memory.
+__device__ __forceinline__ void bitonic_sort(unsigned long long* key, int P)
+{
+  for (int size = 2; size <= P; size <<= 1) {
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      for (int i = threadIdx.x; i < P; i += blockDim.x) {
+        const int j = i ^ stride;
+        if (j > i) {
+          const bool up              = (i & size) == 0;
+          const unsigned long long a = key[i], b = key[j];
+          if ((a > b) == up) {
+            key[i] = b;
+            key[j] = a;
+          }
+        }
+      }
+      __syncthreads();
+    }
+  }
+}
+
+struct radix_cut_t {
+  unsigned long long prefix, mask;
+};
+
+/// Threshold of the R smallest of n distinct 64-bit keys (n > R): 8-bit radix passes from the top
+/// bits, stopping at the first pass whose bucket is taken whole. On return exactly R keys k satisfy
+/// (k & mask) <= prefix. key_at(i) gives key i. All threads of the block call it.
+template <typename KeyAt>
+__device__ __forceinline__ radix_cut_t radix_cut(KeyAt key_at, int n, int R, unsigned* hist, int* ctrl)
+{
+  radix_cut_t c{0ULL, 0ULL};
+  int need = R;
+  for (int shift = 56; shift >= 0; shift -= 8) {
+    for (int i = threadIdx.x; i < 256; i += blockDim.x)
+      hist[i] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      const unsigned long long k = key_at(i);
+      if ((k & c.mask) == c.prefix) atomicAdd(&hist[(k >> shift) & 255], 1u);
+    }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      // lane l owns digits 8l .. 8l+7: the digit at which the running count reaches `need`
+      const int lane = threadIdx.x;
+      unsigned h[8], mine = 0;
+#pragma unroll
+      for (int t = 0; t < 8; t++) {
+        h[t] = hist[8 * lane + t];
+        mine += h[t];
+      }
+      unsigned inc = mine;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const unsigned u = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += u;
+      }
+      const unsigned before = inc - mine;
+      if (before < static_cast<unsigned>(need) && inc >= static_cast<unsigned>(need)) {
+        unsigned cum = before;
+        int d        = 7;
+#pragma unroll
+        for (int t = 0; t < 8; t++) {
+          if (cum + h[t] >= static_cast<unsigned>(need)) {
+            d = t;
+            break;
+          }
+          cum += h[t];
+        }
+        ctrl[1] = 8 * lane + d;                  // digit
+        ctrl[2] = need - static_cast<int>(cum);  // still needed from that bucket
+        ctrl[3] = static_cast<int>(h[d]);        // bucket size
+      }
+    }
+    __syncthreads();
+    const int digit = ctrl[1], left = ctrl[2], bucket = ctrl[3];
+    c.prefix |= static_cast<unsigned long long>(digit) << shift;
+    c.mask |= 255ULL << shift;
+    need = left;
+    __syncthreads();
+    if (bucket == left) break;
+  }
+  return c;
+}
+
+/// Sixteen int8 codes against sixteen (scale, query) pairs: sum of (code * scale - q)^2 with two
+/// fused multiply-adds per code, in code order. The int8 -> float conversion goes through the
+/// mantissa of 2^23 (exact for every int8 value), which keeps it off the conversion pipe.
+__device__ __forceinline__ float sketch_chunk(const int4& w, const float* __restrict__ sc,
+                                              const float* __restrict__ qv)
+{
+  const unsigned* u = reinterpret_cast<const unsigned*>(&w);
+  float d           = 0.f;
+#pragma unroll
+  for (int wd = 0; wd < 4; wd++) {
+    const unsigned x = u[wd] ^ 0x80808080u;  // code + 128 in every byte
+    const float4 s4  = *reinterpret_cast<const float4*>(sc + 4 * wd);
+    const float4 q4  = *reinterpret_cast<const float4*>(qv + 4 * wd);
+    const float s[4] = {s4.x, s4.y, s4.z, s4.w};
+    const float q[4] = {q4.x, q4.y, q4.z, q4.w};
+#pragma unroll
+    for (int b = 0; b < 4; b++) {
+      const float code =
+        __fadd_rn(__uint_as_float(__byte_perm(x, 0x4B000000u, 0x7650 + b)), -8388736.0f);
+      const float t = __fmaf_rn(code, s[b], -q[b]);
+      d             = __fmaf_rn(t, t, d);
+    }
+  }
+  return d;
+}
+
+/// Squared distances of the fp16 rows sid[0, ns) (entries < 0 are skipped) to the fp32 query fq,
+/// written over sdv. Summation order (shared with the CPU checker): element pair k feeds partial
+/// sum k mod 32 with two fused multiply-adds; a butterfly over the 32 partial sums
+/// (search_kernels.cuh:325-342 is the reference's warp-per-row form of the same sum). Eight lanes
+/// own a row, each reading 16 bytes per step; a warp works on eight rows at a time.
+__device__ __forceinline__ void exact_distances(
+  const int* sid, int ns, const __half* __restrict__ vectors, int D, const float* fq, float* sdv)
+{
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  if ((D & 7) == 0) {
+    const int sub = lane & 7, grp = lane >> 3;
+    for (int jb = 0; jb < ns; jb += nw * 8) {
+      int j[2];
+      const uint4* row[2];
+      float acc[2][4];
+#pragma unroll
+      for (int u = 0; u < 2; u++) {
+        j[u]         = jb + u * nw * 4 + warp * 4 + grp;
+        const int id = j[u] < ns ? sid[j[u]] : -1;
+        row[u] = id >= 0 ? reinterpret_cast<const uint4*>(vectors + static_cast<int64_t>(id) * D) : nullptr;
+#pragma unroll
+        for (int t = 0; t < 4; t++)
+          acc[u][t] = 0.f;
+      }
+      // two 16-byte steps of both rows are loaded before any of them is used
+      for (int h0 = 8 * sub; h0 < D; h0 += 128) {
+        uint4 v[2][2];
+#pragma unroll
+        for (int s = 0; s < 2; s++)
+#pragma unroll
+          for (int u = 0; u < 2; u++)
+            if (row[u] != nullptr && h0 + 64 * s < D) v[s][u] = __ldg(row[u] + ((h0 + 64 * s) >> 3));
+#pragma unroll
+        for (int s = 0; s < 2; s++) {
+          const int hs = h0 + 64 * s;
+          if (hs >= D) break;
+#pragma unroll
+          for (int u = 0; u < 2; u++) {
+            if (row[u] == nullptr) continue;
+            const __half2* h2 = reinterpret_cast<const __half2*>(&v[s][u]);
+#pragma unroll
+            for (int t = 0; t < 4; t++) {
+              const float2 x = __half22float2(h2[t]);
+              const float a  = __fsub_rn(x.x, fq[hs + 2 * t]);
+              const float b  = __fsub_rn(x.y, fq[hs + 2 * t + 1]);
+              acc[u][t]      = __fmaf_rn(b, b, __fmaf_rn(a, a, acc[u][t]));
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 2; u++) {
+#pragma unroll
+        for (int o = 4; o; o >>= 1)
+#pragma unroll
+          for (int t = 0; t < 4; t++)
+            acc[u][t] = __fadd_rn(acc[u][t], __shfl_xor_sync(0xffffffffu, acc[u][t], o));
+        if (row[u] != nullptr && sub == 0)
+          sdv[j[u]] = __fadd_rn(__fadd_rn(acc[u][0], acc[u][2]), __fadd_rn(acc[u][1], acc[u][3]));
+      }
+    }
+  } else {
+    for (int j = warp; j < ns; j += nw) {
+      if (sid[j] < 0) continue;
+      const __half2* row = reinterpret_cast<const __half2*>(vectors + static_cast<int64_t>(sid[j]) * D);
+      float acc          = 0.f;
+      for (int k = lane; k < D / 2; k += 32) {
+        const float2 x = __half22float2(row[k]);
+        const float a  = __fsub_rn(x.x, fq[2 * k]);
+        const float b  = __fsub_rn(x.y, fq[2 * k + 1]);
+        acc            = __fmaf_rn(b, b, __fmaf_rn(a, a, acc));
+      }
+#pragma unroll
+      for (int o = 16; o; o >>= 1)
+        acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, o));
+      if (lane == 0) sdv[j] = acc;
+    }
+  }
+  __syncthreads();
+}
+
+/// Merge the new (distance, id) pairs sid / sdv [0, ns) (entries with sid < 0 are skipped; no id is
+/// in the kept list already) into the kept list pb / pd of KO: the KO smallest keys, ascending,
+/// padded with (-1, +inf). Same result as sorting kept + new and taking the first KO distinct keys
+/// (search_kernels.cuh:372-415); here the KO smallest are cut out by radix passes and only they are
+/// sorted. pool holds KO + ns keys, sorted holds P (power of two >= KO).
+__device__ __forceinline__ void merge_into_kept(unsigned long long* pool,
+                                                unsigned long long* sorted,
+                                                int P,
+                                                long long* pb,
+                                                float* pd,
+                                                int KO,
+                                                const int* kid,
+                                                const float* kd,
+                                                const int* sid,
+                                                const float* sdv,
+                                                int ns,
+                                                unsigned* hist,
+                                                int* ctrl)
+{
+  // kid / kd: the kept list as it was (shared memory), null when it starts empty
+  const bool fresh = kid == nullptr;
+  if (threadIdx.x == 0) ctrl[6] = 0;
+  __syncthreads();
+  // the kept list is packed (valid entries first), new keys are appended behind KO in any order
+  for (int i = threadIdx.x; i < KO; i += blockDim.x)
+    pool[i] = (!fresh && kid[i] >= 0) ? rank_key(kd[i], static_cast<unsigned>(kid[i])) : kNoKey;
+  for (int i = threadIdx.x; i < ns; i += blockDim.x)
+    if (sid[i] >= 0) pool[KO + atomicAdd(&ctrl[6], 1)] = rank_key(sdv[i], static_cast<unsigned>(sid[i]));
+  __syncthreads();
+  const int nn = ctrl[6];
+  int nk       = 0;
+  if (!fresh) {  // number of valid kept entries: first index holding no key
+    int lo = 0, hi = KO;
+    while (lo < hi) {
+      const int mid = (lo + hi) >> 1;
+      if (pool[mid] != kNoKey)
+        lo = mid + 1;
+      else
+        hi = mid;
+    }
+    nk = lo;
+  }
+  const int total = nk + nn;
+  auto key_at     = [&](int i) { return i < nk ? pool[i] : pool[KO + (i - nk)]; };
+  int cnt         = total;
+  if (total > KO) {
+    const radix_cut_t c = radix_cut(key_at, total, KO, hist, ctrl);
+    if (threadIdx.x == 0) ctrl[0] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < total; i += blockDim.x) {
+      const unsigned long long k = key_at(i);
+      if ((k & c.mask) <= c.prefix) {
+        const int s = atomicAdd(&ctrl[0], 1);
+        if (s < P) sorted[s] = k;
+      }
+    }
+    cnt = KO;
+  } else {
+    for (int i = threadIdx.x; i < total; i += blockDim.x)
+      sorted[i] = key_at(i);
+  }
+  for (int i = cnt + threadIdx.x; i < P; i += blockDim.x)
+    sorted[i] = kNoKey;
+  __syncthreads();
+  bitonic_sort(sorted, P);
+  for (int i = threadIdx.x; i < KO; i += blockDim.x) {
+    const unsigned long long k = i < cnt ? sorted[i] : kNoKey;
+    pb[i] = k == kNoKey ? -1 : static_cast<long long>(static_cast<unsigned>(k & 0xffffffffULL));
+    pd[i] = k == kNoKey ? INFINITY : __uint_as_float(static_cast<unsigned>(k >> 32));
+  }
+}
+
+template <bool kRows>
+__global__ void __launch_bounds__(kRoundThreads, 5) round_kernel(const round_args a)
+{
+  extern __shared__ __align__(16) int smem[];
+  const round_layout lay(a);
+  const int q = blockIdx.x;
+  int* table  = smem + lay.table;
+  int* cand   = a.cand_global ? a.cand_global + static_cast<int64_t>(q) * a.nmax : smem + lay.cand;
+  float* dist = a.dist_global ? a.dist_global + static_cast<int64_t>(q) * a.nmax
+                              : reinterpret_cast<float*>(smem + lay.dist);
+  unsigned long long* pool   = reinterpret_cast<unsigned long long*>(smem + lay.pool);
+  unsigned long long* sorted = reinterpret_cast<unsigned long long*>(smem + lay.sorted);
+  int* sid                   = smem + lay.sid;
+  float* sdv                 = reinterpret_cast<float*>(smem + lay.sdv);
+  float* qv                  = reinterpret_cast<float*>(smem + lay.qv);
+  float* sc                  = reinterpret_cast<float*>(smem + lay.sc);
+  float* fq                  = reinterpret_cast<float*>(smem + lay.fq);
+  int* st                    = smem + lay.st;
+  int* len                   = smem + lay.len;
+  unsigned* hist             = reinterpret_cast<unsigned*>(smem + lay.hist);
+  int* wsum                  = smem + lay.wsum;
+  int* ctrl                  = smem + lay.ctrl;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int S    = a.sw;
+  long long* pb  = a.si + static_cast<int64_t>(q) * a.KO;
+  float* pd      = a.sd + static_cast<int64_t>(q) * a.KO;
+  const bool fresh = a.fresh != 0;
+
+  for (int i = threadIdx.x; i < S; i += blockDim.x) {
+    qv[i] = a.qs[static_cast<int64_t>(q) * S + i];
+    sc[i] = a.scale[i];
+  }
+  if (!a.sketch_rank)
+    for (int i = threadIdx.x; i < a.D; i += blockDim.x)
+      fq[i] = a.Q[static_cast<int64_t>(q) * a.D + i];
+  if (threadIdx.x == 0) ctrl[4] = 0;  // distinct ids
+  // the kept list as the round finds it: read once, used by the start points, by the filter of
+  // already kept ids and by the merge
+  int* kid  = smem + lay.kid;
+  float* kd = reinterpret_cast<float*>(smem + lay.kd);
+  if (!fresh)
+    for (int i = threadIdx.x; i < a.KO; i += blockDim.x) {
+      kid[i] = static_cast<int>(pb[i]);
+      kd[i]  = pd[i];
+    }
+
+  int total = 0, nseg = a.nseg;
+  if constexpr (kRows) {
+    // start points: the first nseg kept entries that no earlier wave expanded
+    // (search_kernels.cuh:571-631); earlier start points go through a hash set in the table region
+    int* pdone = a.done + static_cast<int64_t>(q) * a.done_stride;
+    for (int i = threadIdx.x; i < a.pick_slots; i += blockDim.x)
+      table[i] = -1;
+    __syncthreads();
+    for (int i = threadIdx.x; i < a.done_off; i += blockDim.x) {
+      const int v = pdone[i];
+      if (v < 0) continue;
+      unsigned h = (static_cast<unsigned>(v) * kIdHash) & (a.pick_slots - 1);
+      for (int p = 0; p < a.pick_slots; p++) {
+        const int prev = atomicCAS(&table[h], -1, v);
+        if (prev == -1 || prev == v) break;
+        h = (h + 1) & (a.pick_slots - 1);
+      }
+    }
+    __syncthreads();
+    const int per       = (a.KO + kRoundThreads - 1) / kRoundThreads;
+    const int i0        = threadIdx.x * per;
+    unsigned fresh_bits = 0;
+    int mine            = 0;
+    for (int i = i0; i < min(a.KO, i0 + per); i++) {
+      const int v = kid[i];
+      bool f      = v >= 0;
+      if (f) {
+        unsigned h = (static_cast<unsigned>(v) * kIdHash) & (a.pick_slots - 1);
+        for (int p = 0; p < a.pick_slots; p++) {
+          const int t = table[h];
+          if (t == -1) break;
+          if (t == v) {
+            f = false;
+            break;
+          }
+          h = (h + 1) & (a.pick_slots - 1);
+        }
+      }
+      if (f) {
+        fresh_bits |= 1u << (i - i0);
+        mine++;
+      }
+    }
+    int nfresh = 0;
+    int at     = block_scan(mine, wsum, nfresh);
+    for (int i = i0; i < min(a.KO, i0 + per); i++)
+      if (fresh_bits & (1u << (i - i0))) {
+        if (at < a.nseg) {
+          const int v            = kid[i];
+          st[at]                 = v;
+          pdone[a.done_off + at] = v;
+        }
+        at++;
+      }
+    nseg = min(nfresh, a.nseg);
+    for (int o = nseg + threadIdx.x; o < a.nseg; o += blockDim.x)
+      pdone[a.done_off + o] = -1;
+    total = nseg * a.table_len;
+    if (threadIdx.x == 0) ctrl[5] = nseg;
+    __syncthreads();
+  } else {
+    // segment starts and lengths; every segment is either empty or `read` entries long
+    int mine = 0;
+    for (int c = threadIdx.x; c < a.nseg; c += blockDim.x) {
+      const int2 sl = a.seg[static_cast<int64_t>(q) * a.nseg + c];
+      st[c]         = sl.x;
+      len[c]        = sl.y;
+      mine += sl.y;
+    }
+    block_scan(mine, wsum, total);
+  }
+
+  // distinct ids through an open-addressing hash set (search_kernels.cuh:191-225); a group of lps
+  // threads walks one segment, so consecutive threads read consecutive entries, and every thread
+  // has four segments' loads in flight before it touches the set
+  const int HT = 1 << hash_log_of(total, a.log_cap);
+  for (int i = threadIdx.x; i < HT; i += blockDim.x)
+    table[i] = -1;
+  __syncthreads();
+  {
+    const int maxlen = kRows ? a.table_len : a.lr;
+    int lps          = 1;
+    while (lps < maxlen && lps < kRoundThreads)
+      lps <<= 1;
+    const int within0 = threadIdx.x & (lps - 1);
+    const int spp     = kRoundThreads / lps;  // segments per pass
+    const int seg0    = threadIdx.x / lps;
+    for (int w0 = within0; w0 < maxlen; w0 += lps) {
+      for (int sb = seg0; sb < nseg; sb += 4 * spp) {
+        int v[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+          const int s = sb + u * spp;
+          v[u]        = -1;
+          if (s < nseg) {
+            if constexpr (kRows) {
+              v[u] = __ldg(a.table + static_cast<int64_t>(st[s]) * a.table_len + w0);
+            } else {
+              if (w0 < len[s]) v[u] = __ldg(a.lists + static_cast<int64_t>(s) * a.stride + st[s] + w0);
+            }
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+          const int id = v[u];
+          if (id < 0) continue;  // nothing read, or the padding of a table row
+          unsigned s = (static_cast<unsigned>(id) * kIdHash) & (HT - 1);
+          for (int p = 0; p < HT; p++) {
+            const int prev = atomicCAS(&table[s], -1, id);
+            if (prev == -1) {
+              const int slot = atomicAdd(&ctrl[4], 1);
+              if (slot < a.nmax) cand[slot] = id;
+              // the sketch row of a new id will be wanted soon: start bringing it into L2
+              asm volatile("prefetch.global.L2 [%0];" ::"l"(a.sketch + static_cast<int64_t>(id) * S));
+              break;
+            }
+            if (prev == id) break;
+            s = (s + 1) & (HT - 1);
+          }
+        }
+      }
+    }
+  }
+  __syncthreads();
+  const int n = min(ctrl[4], a.nmax);
+
+  // int8 sketch distances (search_kernels.cuh:228-251): Lr lanes per row, one 16-byte chunk each,
+  // four rows per lane group in flight
+  {
+    int Lr = 1;
+    while (Lr < S / 16 && Lr < 32)
+      Lr <<= 1;
+    const int G = 32 / Lr, sub = lane % Lr;
+    const int rpp    = nw * G;  // rows per pass of the block
+    const bool live  = sub * 16 < S;
+    const float* scl = sc + (live ? sub * 16 : 0);
+    const float* qvl = qv + (live ? sub * 16 : 0);
+    for (int jb = 0; jb < n; jb += 4 * rpp) {
+      int4 w[4];
+      int j[4];
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+        j[u] = jb + u * rpp + warp * G + lane / Lr;
+        if (j[u] < n && live)
+          w[u] = __ldg(reinterpret_cast<const int4*>(a.sketch + static_cast<int64_t>(cand[j[u]]) * S + sub * 16));
+      }
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+        float d = (j[u] < n && live) ? sketch_chunk(w[u], scl, qvl) : 0.f;
+        for (int o = Lr >> 1; o; o >>= 1)
+          d = __fadd_rn(d, __shfl_xor_sync(0xffffffffu, d, o));
+        if (j[u] < n && sub == 0) dist[j[u]] = d;
+      }
+    }
+  }
+  __syncthreads();
+  if (a.tap_cand != nullptr) {
+    for (int i = threadIdx.x; i < min(n, a.tap_cap); i += blockDim.x) {
+      a.tap_cand[static_cast<int64_t>(q) * a.tap_cap + i] = cand[i];
+      a.tap_dist[static_cast<int64_t>(q) * a.tap_cap + i] = dist[i];
+    }
+    if (threadIdx.x == 0) a.tap_n[q] = n;
+  }
+
+  // the nearest by (sketch distance, id) (search_kernels.cuh:259-322 takes equal distances at the
+  // cut in any order)
+  const int R = a.sketch_rank ? a.KO : a.R;
+  int ns      = n;
+  if (n > R) {
+    auto key_at = [&](int i) { return rank_key(dist[i], static_cast<unsigned>(cand[i])); };
+    const radix_cut_t c = radix_cut(key_at, n, R, hist, ctrl);
+    if (threadIdx.x == 0) ctrl[0] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      if ((key_at(i) & c.mask) <= c.prefix) {
+        const int s = atomicAdd(&ctrl[0], 1);
+        if (s < R) {
+          sid[s] = cand[i];
+          sdv[s] = dist[i];
+        }
+      }
+    }
+    ns = R;
+  } else {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      sid[i] = cand[i];
+      sdv[i] = dist[i];
+    }
+  }
+  __syncthreads();
+
+  // a selected id that is already in the kept list brings the key it already has there: drop it
+  // before the vectors are read (the reference reranks it again and collapses the equal keys)
+  if (!fresh) {
+    int HK = 64;
+    while (HK < 2 * a.KO)
+      HK <<= 1;
+    for (int i = threadIdx.x; i < HK; i += blockDim.x)
+      table[i] = -1;
+    __syncthreads();
+    for (int i = threadIdx.x; i < a.KO; i += blockDim.x) {
+      const int v = kid[i];
+      if (v < 0) continue;
+      unsigned h = (static_cast<unsigned>(v) * kIdHash) & (HK - 1);
+      for (int p = 0; p < HK; p++) {
+        const int prev = atomicCAS(&table[h], -1, v);
+        if (prev == -1 || prev == v) break;
+        h = (h + 1) & (HK - 1);
+      }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < ns; i += blockDim.x) {
+      const int v = sid[i];
+      unsigned h  = (static_cast<unsigned>(v) * kIdHash) & (HK - 1);
+      for (int p = 0; p < HK; p++) {
+        const int t = table[h];
+        if (t == -1) break;
+        if (t == v) {
+          sid[i] = -1;
+          break;
+        }
+        h = (h + 1) & (HK - 1);
+      }
+    }
+    __syncthreads();
+  }
+  int reranked = 0;
+  if (!a.sketch_rank) {
+    // every row about to be read is asked for at once (128-byte lines into L2), so the distance
+    // loop below finds most of them on the way
+    const int lines = (a.D * 2 + 127) >> 7;
+    for (int i = threadIdx.x; i < ns * lines; i += blockDim.x) {
+      const int r = i / lines;
+      if (sid[r] < 0) continue;
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(
+        reinterpret_cast<const char*>(a.vectors + static_cast<int64_t>(sid[r]) * a.D) + 128 * (i - r * lines)));
+    }
+    if (a.stats != nullptr) {
+      int mine = 0;
+      for (int i = threadIdx.x; i < ns; i += blockDim.x)
+        mine += sid[i] >= 0;
+      block_scan(mine, wsum, reranked);
+    }
+    exact_distances(sid, ns, a.vectors, a.D, fq, sdv);
+  }
+  merge_into_kept(pool, sorted, a.P, pb, pd, a.KO, fresh ? nullptr : kid, kd, sid, sdv, ns, hist, ctrl);
+  if (a.stats != nullptr && threadIdx.x == 0) {
+    long long* s = a.stats + static_cast<int64_t>(q) * 8;
+    if constexpr (kRows) {
+      s[4] += ctrl[5];
+      s[5] += n;
+    } else {
+      s[2] += total;
+      s[3] += n;
+    }
+    if (!a.sketch_rank) s[6] += ns;  // rows the reference reranks
+    s[7] += reranked;  // rows read here (those already kept are skipped)
+  }
+}
+
+// search_kernels.cuh:634-669: exact distances of the first R kept entries, best k of them.
+__global__ void __launch_bounds__(kRoundThreads) final_rerank_kernel(const long long* __restrict__ si,
+                                                                     int KO,
+                                                                     int R,
+                                                                     const __half* __restrict__ vectors,
+                                                                     int D,
+                                                                     const float* __restrict__ Q,
+                                                                     int k,
+                                                                     int P,
+                                                                     long long* __restrict__ bi,
+                                                                     float* __restrict__ bd,
+                                                                     long long* __restrict__ stats)
+{
+  extern __shared__ __align__(16) int smem[];
+  unsigned long long* pool   = reinterpret_cast<unsigned long long*>(smem);  // [k + R]
+  unsigned long long* sorted = pool + ((k + R + 1) & ~1);                    // [P]
+  int* sid                   = reinterpret_cast<int*>(sorted + P);           // [R]
+  float* sdv                 = reinterpret_cast<float*>(sid + ((R + 3) & ~3));
+  float* fq                  = sdv + ((R + 3) & ~3);                         // [D]
+  unsigned* hist             = reinterpret_cast<unsigned*>(fq + ((D + 3) & ~3));
+  int* wsum                  = reinterpret_cast<int*>(hist + 256);
+  int* ctrl                  = wsum + 16;
+  const int q                = blockIdx.x;
+  const long long* ps        = si + static_cast<int64_t>(q) * KO;
+  for (int i = threadIdx.x; i < D; i += blockDim.x)
+    fq[i] = Q[static_cast<int64_t>(q) * D + i];
+  // the kept list is packed (valid entries first), so the valid ones among the first R are a prefix
+  int mine = 0;
+  for (int i = threadIdx.x; i < R; i += blockDim.x) {
+    const long long v = ps[i];
+    sid[i]            = static_cast<int>(v);
+    if (v >= 0) mine++;
+  }
+  int ns = 0;
+  block_scan(mine, wsum, ns);
+  exact_distances(sid, ns, vectors, D, fq, sdv);
+  merge_into_kept(pool, sorted, P, bi + static_cast<int64_t>(q) * k, bd + static_cast<int64_t>(q) * k,
+                  k, nullptr, nullptr, sid, sdv, ns, hist, ctrl);
+  if (stats != nullptr && threadIdx.x == 0) {
+    stats[static_cast<int64_t>(q) * 8 + 6] += ns;
+    stats[static_cast<int64_t>(q) * 8 + 7] += ns;
+  }
+}
+
+// search_kernels.cuh:517-564: kept lists of nsrc sources -> the nearest copy of each id -> best
+// KO. The sources are rows of arrays in this GPU's own memory (the exchange brought them here).
+__global__ void merge_kept_kernel(const long long* __restrict__ src_i,
+                                  const float* __restrict__ src_d,
+                                  int nsrc,
+                                  int64_t src_stride,
+                                  int KO,
+                                  int P,
+                                  long long* __restrict__ si,
+                                  float* __restrict__ sd)
+{
+  extern __shared__ __align__(16) int smem[];
+  unsigned long long* mk = reinterpret_cast<unsigned long long*>(smem);
+  const int q            = blockIdx.x;
+  const int total        = nsrc * KO;
+  for (int i = threadIdx.x; i < P; i += blockDim.x) {
+    unsigned long long k = kNoKey;
+    if (i < total) {
+      const int h       = i / KO;
+      const int64_t at  = h * src_stride + static_cast<int64_t>(q) * KO + i % KO;
+      const long long v = src_i[at];
+      if (v >= 0)
+        k = (static_cast<unsigned long long>(static_cast<unsigned>(v)) << 32) | __float_as_uint(src_d[at]);
+    }
+    mk[i] = k;
+  }
+  __syncthreads();
+  bitonic_sort(mk, P);  // by (id, distance): the first key of an id run is its nearest copy
+  const int per = (P + kRoundThreads - 1) / kRoundThreads;
+  const int i0  = threadIdx.x * per;
+  unsigned long long mine[16];
+  int cnt = 0;
+  for (int i = i0; i < min(P, i0 + per); i++) {
+    const unsigned long long k = mk[i];
+    unsigned long long out     = kNoKey;
+    if (k != kNoKey && (i == 0 || (mk[i - 1] >> 32) != (k >> 32)))
+      out = ((k & 0xffffffffULL) << 32) | (k >> 32);
+    mine[cnt++] = out;
+  }
+  __syncthreads();
+  cnt = 0;
+  for (int i = i0; i < min(P, i0 + per); i++)
+    mk[i] = mine[cnt++];
+  __syncthreads();
+  bitonic_sort(mk, P);  // by (distance, id)
+  long long* pb = si + static_cast<int64_t>(q) * KO;
+  float* pd     = sd + static_cast<int64_t>(q) * KO;
+  for (int i = threadIdx.x; i < KO; i += blockDim.x) {
+    const unsigned long long k = mk[i];
+    pb[i] = k == kNoKey ? -1 : static_cast<long long>(static_cast<unsigned>(k & 0xffffffffULL));
+    pd[i] = k == kNoKey ? INFINITY : __uint_as_float(static_cast<unsigned>(k >> 32));
+  }
+}
+
+}  // namespace
+
+size_t round_smem_bytes(const round_args& a) { return sizeof(int) * round_layout(a).words; }
+
+void round_allow_smem(size_t bytes)
+{
+  cudaFuncSetAttribute(round_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                       static_cast<int>(bytes));
+  cudaFuncSetAttribute(round_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                       static_cast<int>(bytes));
+}
+
+void round_lists(const round_args& a, cudaStream_t s)
+{
+  if (a.m <= 0) return;
+  round_kernel<false><<<a.m, kRoundThreads, round_smem_bytes(a), s>>>(a);
+}
+
+void round_rows(const round_args& a, cudaStream_t s)
+{
+  if (a.m <= 0) return;
+  round_kernel<true><<<a.m, kRoundThreads, round_smem_bytes(a), s>>>(a);
+}
+
+void final_rerank(const long long* si, int KO, int R, const __half* vectors, int D, const float* Q,
+                  int k, int m, long long* bi, float* bd, long long* stats, cudaStream_t s)
+{
+  if (m <= 0) return;
+  int P = 2;
+  while (P < k)
+    P <<= 1;
+  const size_t words = 2 * static_cast<size_t>((k + R + 1) & ~1) + 2 * static_cast<size_t>(P) +
+                       2 * static_cast<size_t>((R + 3) & ~3) + ((D + 3) & ~3) + 256 + 16 + 8;
+  final_rerank_kernel<<<m, kRoundThreads, sizeof(int) * words, s>>>(si, KO, R, vectors, D, Q, k, P, bi,
+                                                                    bd, stats);
+}
+
+void merge_kept(const long long* src_i, const float* src_d, int nsrc, int64_t src_stride, int KO,
+                int P, int m, long long* si, float* sd, cudaStream_t s)
+{
+  if (m <= 0) return;
+  static bool allowed = false;
+  const size_t smem   = sizeof(int) * (2 * static_cast<size_t>(P) + 16);
+  if (!allowed) {
+    cudaFuncSetAttribute(merge_kept_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 4096 + 64);
+    allowed = true;
+  }
+  merge_kept_kernel<<<m, kRoundThreads, smem, s>>>(src_i, src_d, nsrc, src_stride, KO, P, si, sd);
+}
+
+}  // namespace octex_b200::kernels

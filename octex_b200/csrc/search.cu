@@ -51,9 +51,8 @@ void size_round(plan& pl, kernels::round_args& r, int entries_max, int pick_entr
   }
   r.ht_slots = std::max(1 << r.log_cap, r.pick_slots);
   r.nmax     = std::max(entries_max, 1);
-  const int rm = r.sketch_rank ? r.KO : r.R;
   r.P = 2;
-  while (r.P < r.KO + rm)
+  while (r.P < r.KO)
     r.P <<= 1;
   r.cand_global = nullptr;
   r.dist_global = nullptr;
@@ -249,6 +248,7 @@ auto make_plan(index_impl& ix, search_params const& sp, int m, int k, debug_opti
   r1.seg         = pl.seg.as<int2>();
   r1.lists       = p.lists.as<int>();
   r1.stride      = p.stride;
+  r1.lr          = pl.lr;
   r1.sketch      = p.sketch.as<signed char>();
   r1.scale       = p.scale.as<float>();
   r1.qs          = pl.qs.as<float>();

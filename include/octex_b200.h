@@ -248,6 +248,32 @@ OCTEX_B200_EXPORT cuvsError_t octexB200Fetch(cuvsOctexIndex_t index, const char*
 OCTEX_B200_EXPORT cuvsError_t octexB200CellCodes(const float* y, int64_t n, int32_t blocks,
                                                  float inv_f, int64_t* codes);
 
+/* Cell codes of a batch of queries, computed without allocating anything. No counterpart in the
+ * reference: its search always allocates its per-batch buffers (cpp/src/neighbors/octex/search.cu
+ * does so in make_plan). This call is for callers that must not allocate device memory where they
+ * stand: a process whose device memory was all given to one arena at start-up (a later cudaMalloc
+ * fails, or is against the rules of that process), a serving loop that cannot take the device-wide
+ * synchronisation a cudaMalloc / cudaFree pair brings, and code that runs while a stream capture
+ * is open elsewhere in the process, where cudaMalloc is not allowed.
+ *
+ * queries [n_queries, dim] float32 and codes [n_queries, copies, levels] int64 are DEVICE memory on
+ * the GPU of the index, which must be the current device; the work is queued on `stream` (a
+ * cudaStream_t, NULL for the default stream) and codes[q][c][j] is the code of query q's cell in
+ * copy c at spacing j, every level computed (the array octexB200Fetch calls "codes").
+ *
+ * The intermediates (centred fp16 queries, sketch-space queries, fp16 projected coordinates) live
+ * in one fixed 32 MiB array inside the library, which every GPU that loads the library holds until
+ * the process ends. A call whose n_queries * (2 * dim64 + 4 * sketch_width + 16 * blocks * copies)
+ * bytes (dim64 = dim rounded up to 64) exceed 32 MiB is refused with CUVS_ERROR and a message that
+ * names the largest batch that fits. All calls on a GPU share that array: it holds whatever the
+ * last call left (each call overwrites every byte it later reads, nothing needs clearing), and two
+ * calls that overlap on the GPU (different streams, no ordering between them) race on it. The
+ * first call on each GPU looks up the array's device address; make that first call outside of any
+ * stream capture. */
+OCTEX_B200_EXPORT cuvsError_t octexB200QueryCodesStatic(cuvsOctexIndex_t index,
+                                                        const float* queries, int64_t n_queries,
+                                                        int64_t* codes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -88,7 +88,8 @@ SYMBOLS = (
     "cuvsOctexIndexGetDim", "cuvsOctexIndexGetCopies", "cuvsOctexIndexGetNumDevices",
     "cuvsOctexIndexGetDevices", "cuvsOctexIndexGetDeviceBytes", "cuvsOctexBuild", "cuvsOctexLoad",
     "cuvsOctexSearch", "octexB200Search", "octexB200LoadRank", "octexB200Attach",
-    "octexB200SearchResident", "octexB200ProfileBatch", "octexB200SetDebug", "octexB200Fetch", "octexB200CellCodes",
+    "octexB200SearchResident", "octexB200ProfileBatch", "octexB200SetDebug", "octexB200Fetch",
+    "octexB200CellCodes", "octexB200QueryCodesStatic",
 )
 
 

@@ -236,6 +236,11 @@ OCTEX_B200_EXPORT cuvsError_t octexB200ProfileBatch(cuvsResources_t res,
  * counterparts): stats = per-query counters of what the kernels read, taps = keep the intermediate
  * arrays of the last batch. Either one changes the plan; both are off by default. */
 OCTEX_B200_EXPORT cuvsError_t octexB200SetDebug(cuvsOctexIndex_t index, int32_t stats, int32_t taps);
+/* The projection of the queries (the cuBLASLt call of cpp/src/neighbors/octex/search.cu:303-320)
+ * runs on the tensor cores by default. ordered = 1 selects the kernel that accumulates every dot
+ * product in dimension order instead, whose projected coordinates a CPU implementation can
+ * reproduce bit for bit (parity tests use it); 0 goes back. Changes the plan. */
+OCTEX_B200_EXPORT cuvsError_t octexB200SetProjection(cuvsOctexIndex_t index, int32_t ordered);
 /* Copy a named array of the last batch to host memory: "y", "qs", "codes", "seg", "cand1",
  * "cand1_dist", "n1", "kept1_ids", "kept1_dist", "stats", "kept_ids", "kept_dist". *bytes returns
  * its size; dst may be NULL to ask for the size only. */

@@ -89,7 +89,7 @@ SYMBOLS = (
     "cuvsOctexIndexGetDevices", "cuvsOctexIndexGetDeviceBytes", "cuvsOctexBuild", "cuvsOctexLoad",
     "cuvsOctexSearch", "octexB200Search", "octexB200LoadRank", "octexB200Attach",
     "octexB200SearchResident", "octexB200ProfileBatch", "octexB200SetDebug", "octexB200Fetch",
-    "octexB200CellCodes", "octexB200QueryCodesStatic",
+    "octexB200CellCodes", "octexB200QueryCodesStatic", "octexB200SetProjection",
 )
 
 

@@ -432,6 +432,15 @@ cuvsError_t octexB200SetDebug(cuvsOctexIndex_t index, int32_t stats, int32_t tap
   });
 }
 
+cuvsError_t octexB200SetProjection(cuvsOctexIndex_t index, int32_t ordered)
+{
+  return translate([=] {
+    auto& ix = as_index(*index)->impl();
+    std::lock_guard<std::mutex> lock(ix.mu);
+    ix.debug.ordered_projection = ordered != 0;
+  });
+}
+
 cuvsError_t octexB200Fetch(cuvsOctexIndex_t index, const char* name, void* dst, int64_t capacity,
                            int64_t* bytes)
 {
@@ -457,6 +466,8 @@ cuvsError_t octexB200Fetch(cuvsOctexIndex_t index, const char* name, void* dst, 
     else if (n == "kept_ids") b = &pl->si;
     else if (n == "kept_dist") b = &pl->sd;
     else if (n == "stats") b = &pl->stats;
+    else if (n == "phase_lists") b = &pl->phase1;
+    else if (n == "phase_rows") b = &pl->phase2;
     OCTEX_EXPECTS(b != nullptr, "octex: unknown array name \"" + n + "\"");
     OCTEX_EXPECTS(b->ptr != nullptr, "octex: \"" + n + "\" is not kept (see octexB200SetDebug)");
     if (bytes != nullptr) *bytes = static_cast<int64_t>(b->size);

@@ -34,6 +34,9 @@ struct plan;
 struct debug_options {
   bool stats = false;  ///< per-query counters of what the kernels read
   bool taps  = false;  ///< keep the intermediate arrays of the last batch for inspection
+  /// Project with the kernel that sums in dimension order (bit-comparable with the CPU checker)
+  /// instead of the tensor-core kernel.
+  bool ordered_projection = false;
 };
 
 struct device_part {

@@ -35,6 +35,22 @@ void project_ordered(const __half* qh, int ldq, const __half* ut, int ldu, const
 void decode_codes(const __half* Y, int64_t pairs, int C, int blocks, int L, const float* inv_f,
                   const unsigned char* level_on, long long* codes, cudaStream_t s);
 
+/// Tensor-core projection with the decode in its epilogue (project_tc.cu): TMA tensor maps of the
+/// two operands, made once per plan.
+struct project_tc_plan {
+  alignas(64) unsigned char map_a[128];  // fp16 queries [m, ldu]
+  alignas(64) unsigned char map_b[128];  // fp16 projections [copies * 32, ldu]
+  int m = 0, copies = 0, ldu = 0;
+};
+/// True when the tensor-core kernel covers this index shape (4 blocks per copy).
+bool project_tc_supported(int blocks, int ldu);
+void project_tc_setup(project_tc_plan& p, const __half* qh, int m, const __half* ut, int copies, int ldu);
+/// codes [m, copies, L] (and Yout [m, copies * 32] fp16 when not null) from the operands of the
+/// plan. *error (device-visible int) becomes non-zero when a wait inside the kernel ran out.
+void project_decode_tc(const project_tc_plan& p, int L, const __half* shift, const float* inv_f,
+                       const unsigned char* level_on, long long* codes, __half* Yout, int* error,
+                       cudaStream_t s);
+
 /// codes [n] = cell code of each row of y [n, 8*blocks] float32 scaled by inv_f.
 void cell_codes_f32(const float* y, int64_t n, int blocks, float inv_f, long long* codes,
                     cudaStream_t s);
@@ -89,6 +105,7 @@ struct round_args {
   float* tap_dist = nullptr;  // [m, tap_cap]
   int* tap_n = nullptr;       // [m]
   int tap_cap = 0;
+  long long* phase = nullptr;  // [m, 8] cycles per phase of the block (observation)
   long long* stats = nullptr;  // [m, 8]: [2] entries read, [3] distinct ids first round,
                                // [4] table rows expanded, [5] distinct ids of waves,
                                // [6] rows selected for the exact rerank, [7] of them read

@@ -1,0 +1,332 @@
+// Projection of a query batch on all copies with the E8 decode in the epilogue (sm_100a only):
+//   acc[m, Cg*32] = qh[m, K] . ut[Cg*32, K]^T        tcgen05.mma, fp16 in, fp32 accumulators in TMEM
+//   y = half(acc + shift)                             what the reference's GEMM writes out
+//   codes[q, c, j] = cell code of y[q, c*32 .. c*32+32) at spacing j
+//
+// Answers the cuBLASLt call of the reference (hpdic/octex, cpp/src/neighbors/octex/search.cu:139-168,
+// 303-320: fp16 operands, fp32 accumulate, fp16 bias epilogue, fp16 output) and the decode half of
+// its probe_kernel (detail/search_kernels.cuh:100-114). The projected coordinates never go to
+// memory: a thread of the epilogue owns one query row, reads the 32 accumulator columns of one
+// copy from TMEM (tcgen05.ld 32x32b.x32 hands a lane exactly one copy), rounds them to fp16 and
+// decodes every populated spacing.
+//
+// One 128 x 128 output tile per block of 128 threads. Operand tiles of 128 rows x 64 halves
+// (128 bytes, the swizzle span) come in by TMA (cp.async.bulk.tensor, no cluster forms) into a
+// two-stage ring; one thread issues the copies and the MMAs; every wait on an mbarrier is bounded
+// and a wait that runs out sets an error word, lets the block free its TMEM and return.
+
+#include "kernels.hpp"
+
+#include "e8.cuh"
+
+#include <cuda.h>
+
+#include <cstring>
+#include <stdexcept>
+#include <string>
+
+namespace octex_b200::kernels {
+
+namespace {
+
+constexpr int kTileM    = 128;  // queries per tile = TMEM lanes
+constexpr int kTileN    = 128;  // projected coordinates per tile = 4 copies of 32
+constexpr int kTileK    = 64;   // halves per operand row in a stage (128 bytes)
+constexpr int kStages   = 2;
+constexpr int kThreads  = 128;
+constexpr int kTmemCols = 128;  // fp32 accumulator columns
+constexpr uint32_t kStageBytes = (kTileM + kTileN) * kTileK * 2;
+constexpr uint32_t kSpinLimit  = 1u << 21;  // polls of an mbarrier before giving up
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p)
+{
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count)
+{
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes)
+{
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+
+/// Wait for the phase with the given parity; false when the poll limit ran out or *give_up
+/// (may be null) became non-zero.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const volatile int* give_up = nullptr)
+{
+  const uint32_t addr = smem_u32(bar);
+  for (uint32_t i = 0; i < kSpinLimit; i++) {
+    if (give_up != nullptr && *give_up != 0) return false;
+    uint32_t ok;
+    asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(ok)
+      : "r"(addr), "r"(parity)
+      : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar)
+{
+  asm volatile(
+    "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+    ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
+    : "memory");
+}
+
+/// Shared-memory matrix descriptor of a K-major operand tile written by TMA with the 128-byte
+/// swizzle: rows of 128 bytes, groups of 8 rows 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc(const void* tile)
+{
+  const uint64_t addr = (smem_u32(tile) & 0x3FFFFu) >> 4;
+  return addr | (uint64_t{1} << 16)      // leading byte offset (unused with a swizzle): 16 bytes
+         | (uint64_t{1024 >> 4} << 32)   // stride byte offset: 1024 bytes between 8-row groups
+         | (uint64_t{1} << 46)           // descriptor version of this architecture
+         | (uint64_t{2} << 61);          // layout: 128-byte swizzle
+}
+
+/// D (fp32, TMEM) (+)= A (fp16, K-major) x B^T (fp16, K-major), 128 x 128 x 16.
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc,
+                                         uint32_t accumulate)
+{
+  asm volatile(
+    "{\n\t"
+    ".reg .pred p;\n\t"
+    "setp.ne.b32 p, %4, 0;\n\t"
+    "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t"
+    "}"
+    ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+    : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint64_t* bar)
+{
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+
+struct __align__(1024) tc_smem {
+  __half a[kStages][kTileM * kTileK];
+  __half b[kStages][kTileN * kTileK];
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  uint64_t done;
+  uint32_t tmem_base;
+  int failed;
+  float shift[kTileN];
+  float inv_f[16];
+};
+
+__global__ void __launch_bounds__(kThreads) project_decode_tc_kernel(
+  const __grid_constant__ CUtensorMap map_a,
+  const __grid_constant__ CUtensorMap map_b,
+  int m,
+  int Cg,
+  int L,
+  int nkb,
+  const __half* __restrict__ shift,
+  const float* __restrict__ inv_f,
+  const unsigned char* __restrict__ level_on,
+  long long* __restrict__ codes,
+  __half* __restrict__ Yout,
+  int* __restrict__ error)
+{
+  extern __shared__ unsigned char raw[];
+  tc_smem& sm = *reinterpret_cast<tc_smem*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t{1023});
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile_n = blockIdx.x, tile_m = blockIdx.y;
+  const int N      = Cg * 32;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; s++) {
+      mbar_init(&sm.full[s], 1);
+      mbar_init(&sm.empty[s], 1);
+    }
+    mbar_init(&sm.done, 1);
+    sm.failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  for (int i = threadIdx.x; i < kTileN; i += kThreads) {
+    const int col = tile_n * kTileN + i;
+    sm.shift[i]   = col < N ? __half2float(shift[col]) : 0.f;
+  }
+  if (threadIdx.x < L) sm.inv_f[threadIdx.x] = inv_f[threadIdx.x];
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                   smem_u32(&sm.tmem_base)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = sm.tmem_base;
+
+  if (threadIdx.x == 0) {
+    // instruction descriptor: D fp32, A and B fp16, both K-major, N = 128, M = 128
+    constexpr uint32_t idesc = (1u << 4) | (static_cast<uint32_t>(kTileN >> 3) << 17) |
+                               (static_cast<uint32_t>(kTileM >> 4) << 24);
+    auto load_stage = [&](int kb) {
+      const int s = kb % kStages;
+      mbar_expect_tx(&sm.full[s], kStageBytes);
+      tma_load_2d(sm.a[s], &map_a, kb * kTileK, tile_m * kTileM, &sm.full[s]);
+      tma_load_2d(sm.b[s], &map_b, kb * kTileK, tile_n * kTileN, &sm.full[s]);
+    };
+    for (int kb = 0; kb < min(nkb, kStages); kb++)
+      load_stage(kb);
+    bool ok = true;
+    for (int kb = 0; kb < nkb && ok; kb++) {
+      const int s          = kb % kStages;
+      const uint32_t phase = (kb / kStages) & 1;
+      ok                   = mbar_wait(&sm.full[s], phase);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint64_t da = umma_desc(sm.a[s]), db = umma_desc(sm.b[s]);
+#pragma unroll
+      for (int k = 0; k < kTileK / 16; k++)  // 16 halves = 32 bytes = 2 descriptor units per step
+        umma_f16(tmem, da + 2 * k, db + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+      if (kb + kStages < nkb) {
+        umma_commit(&sm.empty[s]);  // arrives when the MMAs reading this stage are done
+        ok = mbar_wait(&sm.empty[s], phase);
+        if (ok) load_stage(kb + kStages);
+      }
+    }
+    if (ok) {
+      umma_commit(&sm.done);
+    } else {
+      sm.failed = 1;
+      atomicExch(error, 1);
+    }
+  }
+  __syncwarp();
+  // everybody waits for the accumulators (or for the failure mark the issuing thread leaves)
+  const bool ready = mbar_wait(&sm.done, 0, &sm.failed);
+  if (!ready && threadIdx.x == 0) atomicExch(error, 2);
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  __syncwarp();
+
+  const int row = tile_m * kTileM + warp * 32 + lane;
+  for (int cc = 0; cc < kTileN / 32; cc++) {
+    __syncwarp();  // the TMEM load below is a warp-wide instruction
+    uint32_t r[32];
+    const uint32_t taddr = tmem + (static_cast<uint32_t>(warp * 32) << 16) + static_cast<uint32_t>(cc * 32);
+    asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+        "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),
+        "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
+        "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    const int c = tile_n * (kTileN / 32) + cc;
+    if (!ready || row >= m || c >= Cg) continue;
+    float y[32];
+    __align__(16) __half yh[32];
+#pragma unroll
+    for (int i = 0; i < 32; i++) {
+      yh[i] = __float2half_rn(__fadd_rn(__uint_as_float(r[i]), sm.shift[cc * 32 + i]));
+      y[i]  = __half2float(yh[i]);
+    }
+    if (Yout != nullptr) {
+      uint4* dst = reinterpret_cast<uint4*>(Yout + static_cast<int64_t>(row) * N + c * 32);
+#pragma unroll
+      for (int i = 0; i < 4; i++)
+        dst[i] = *reinterpret_cast<const uint4*>(&yh[8 * i]);
+    }
+    long long* out = codes + (static_cast<int64_t>(row) * Cg + c) * L;
+    for (int j = 0; j < L; j++) {
+      long long h = 0;
+      if (level_on == nullptr || level_on[c * L + j]) h = cell_code<4>(y, sm.inv_f[j]);
+      out[j] = h;
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+  }
+}
+
+using encode_fn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                               CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                               CUtensorMapFloatOOBfill);
+
+auto encoder() -> encode_fn
+{
+  static encode_fn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q{};
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q);
+    if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || p == nullptr) {
+      cudaGetLastError();
+      throw std::runtime_error("octex: the driver has no cuTensorMapEncodeTiled");
+    }
+    fn = reinterpret_cast<encode_fn>(p);
+  }
+  return fn;
+}
+
+/// Tensor map of a row-major fp16 matrix [rows, ld] read in boxes of rows_box x 64 halves with the
+/// 128-byte swizzle; rows and columns beyond the matrix read as zero.
+void make_map(void* out, const __half* base, int64_t rows, int64_t ld, int rows_box)
+{
+  CUtensorMap map;
+  const cuuint64_t dims[2]    = {static_cast<cuuint64_t>(ld), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * sizeof(__half)};
+  const cuuint32_t box[2]     = {kTileK, static_cast<cuuint32_t>(rows_box)};
+  const cuuint32_t estr[2]    = {1, 1};
+  CUresult r = encoder()(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(base), dims,
+                         strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    throw std::runtime_error("octex: cuTensorMapEncodeTiled failed (" + std::to_string(static_cast<int>(r)) + ")");
+  static_assert(sizeof(CUtensorMap) == 128, "tensor map size");
+  std::memcpy(out, &map, sizeof(map));
+}
+
+}  // namespace
+
+bool project_tc_supported(int blocks, int ldu) { return blocks == 4 && ldu % kTileK == 0; }
+
+void project_tc_setup(project_tc_plan& p, const __half* qh, int m, const __half* ut, int copies, int ldu)
+{
+  p.m      = m;
+  p.copies = copies;
+  p.ldu    = ldu;
+  make_map(p.map_a, qh, m, ldu, kTileM);
+  make_map(p.map_b, ut, static_cast<int64_t>(copies) * 32, ldu, kTileN);
+  cudaFuncSetAttribute(project_decode_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                       static_cast<int>(sizeof(tc_smem) + 1024));
+}
+
+void project_decode_tc(const project_tc_plan& p, int L, const __half* shift, const float* inv_f,
+                       const unsigned char* level_on, long long* codes, __half* Yout, int* error,
+                       cudaStream_t s)
+{
+  if (p.m <= 0 || p.copies <= 0) return;
+  CUtensorMap a, b;
+  std::memcpy(&a, p.map_a, sizeof(a));
+  std::memcpy(&b, p.map_b, sizeof(b));
+  dim3 grid((p.copies * 32 + kTileN - 1) / kTileN, (p.m + kTileM - 1) / kTileM);
+  project_decode_tc_kernel<<<grid, kThreads, sizeof(tc_smem) + 1024, s>>>(
+    a, b, p.m, p.copies, L, p.ldu / kTileK, shift, inv_f, level_on, codes, Yout, error);
+}
+
+}  // namespace octex_b200::kernels

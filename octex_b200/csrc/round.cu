@@ -415,6 +415,17 @@ __global__ void __launch_bounds__(kRoundThreads, 5) round_kernel(const round_arg
       kd[i]  = pd[i];
     }
 
+  // cycles per phase of this block (observation only): start points / segments, gather, sketch
+  // scoring, selection, filter + prefetch, exact distances, merge
+  long long t_prev = 0;
+  auto tick = [&](int i) {
+    if (a.phase != nullptr && threadIdx.x == 0) {
+      const long long t = clock64();
+      if (i >= 0) a.phase[static_cast<int64_t>(q) * 8 + i] += t - t_prev;
+      t_prev = t;
+    }
+  };
+  tick(-1);
   int total = 0, nseg = a.nseg;
   if constexpr (kRows) {
     // start points: the first nseg kept entries that no earlier wave expanded
@@ -490,6 +501,7 @@ __global__ void __launch_bounds__(kRoundThreads, 5) round_kernel(const round_arg
   // distinct ids through an open-addressing hash set (search_kernels.cuh:191-225); a group of lps
   // threads walks one segment, so consecutive threads read consecutive entries, and every thread
   // has four segments' loads in flight before it touches the set
+  tick(0);
   const int HT = 1 << hash_log_of(total, a.log_cap);
   for (int i = threadIdx.x; i < HT; i += blockDim.x)
     table[i] = -1;
@@ -540,6 +552,7 @@ __global__ void __launch_bounds__(kRoundThreads, 5) round_kernel(const round_arg
   }
   __syncthreads();
   const int n = min(ctrl[4], a.nmax);
+  tick(1);
 
   // int8 sketch distances (search_kernels.cuh:228-251): Lr lanes per row, one 16-byte chunk each,
   // four rows per lane group in flight
@@ -571,6 +584,7 @@ __global__ void __launch_bounds__(kRoundThreads, 5) round_kernel(const round_arg
     }
   }
   __syncthreads();
+  tick(2);
   if (a.tap_cand != nullptr) {
     for (int i = threadIdx.x; i < min(n, a.tap_cap); i += blockDim.x) {
       a.tap_cand[static_cast<int64_t>(q) * a.tap_cap + i] = cand[i];
@@ -606,6 +620,7 @@ __global__ void __launch_bounds__(kRoundThreads, 5) round_kernel(const round_arg
   }
   __syncthreads();
 
+  tick(3);
   // a selected id that is already in the kept list brings the key it already has there: drop it
   // before the vectors are read (the reference reranks it again and collapses the equal keys)
   if (!fresh) {
@@ -658,9 +673,13 @@ __global__ void __launch_bounds__(kRoundThreads, 5) round_kernel(const round_arg
         mine += sid[i] >= 0;
       block_scan(mine, wsum, reranked);
     }
+    tick(4);
     exact_distances(sid, ns, a.vectors, a.D, fq, sdv);
+    tick(5);
   }
   merge_into_kept(pool, sorted, a.P, pb, pd, a.KO, fresh ? nullptr : kid, kd, sid, sdv, ns, hist, ctrl);
+  __syncthreads();
+  tick(6);
   if (a.stats != nullptr && threadIdx.x == 0) {
     long long* s = a.stats + static_cast<int64_t>(q) * 8;
     if constexpr (kRows) {

@@ -79,7 +79,16 @@ plan::~plan()
   cudaSetDevice(device);
   if (graph != nullptr) cudaGraphExecDestroy(graph);
   if (done_ev != nullptr) cudaEventDestroy(done_ev);
+  if (tc_error_host != nullptr) cudaFreeHost(tc_error_host);
   cudaSetDevice(cur);
+}
+
+/// A wait inside the tensor-core projection gave up (it never does unless the GPU misbehaves).
+void check_tc(plan const& pl)
+{
+  OCTEX_EXPECTS(pl.tc_error_host == nullptr || *pl.tc_error_host == 0,
+                "octex: the projection kernel gave up waiting for its operands (code " +
+                  std::to_string(pl.tc_error_host ? *pl.tc_error_host : 0) + ")");
 }
 
 /// Launch every kernel of a batch on s (captured into the graph, or run directly).
@@ -99,17 +108,29 @@ void run_batch(index_impl const& ix, plan& pl, cudaStream_t s, std::vector<cudaE
   const int L    = static_cast<int>(ix.spacings.size());
   const int wdt  = 8 * ix.blocks * p.copies;
   const int64_t T1 = (int64_t{1} << ix.log_buckets) + 1;
-  if (pl.stats.ptr != nullptr) OCTEX_CUDA_TRY(cudaMemsetAsync(pl.stats.ptr, 0, pl.stats.size, s));
+  if (pl.stats.ptr != nullptr) {
+    OCTEX_CUDA_TRY(cudaMemsetAsync(pl.stats.ptr, 0, pl.stats.size, s));
+    OCTEX_CUDA_TRY(cudaMemsetAsync(pl.phase1.ptr, 0, pl.phase1.size, s));
+    OCTEX_CUDA_TRY(cudaMemsetAsync(pl.phase2.ptr, 0, pl.phase2.size, s));
+  }
   mark();
   kernels::center_sketch(pl.qbuf.as<float>(), p.mean.as<float>(), p.basis.as<float>(), pl.m1, D, sw,
                          pl.qh.as<__half>(), p.ldu, pl.qs.as<float>(), s);
   mark();
-  kernels::project_ordered(pl.qh.as<__half>(), p.ldu, p.ut.as<__half>(), p.ldu,
-                           p.shift.as<__half>(), pl.m1, wdt, D, pl.Y.as<__half>(), s);
-  mark();
-  kernels::decode_codes(pl.Y.as<__half>(), int64_t{pl.m1} * p.copies, p.copies, ix.blocks, L,
-                        p.inv_f.as<float>(), pl.dbg.taps ? nullptr : p.level_on.as<unsigned char>(),
-                        pl.codes.as<long long>(), s);
+  const unsigned char* levels = pl.dbg.taps ? nullptr : p.level_on.as<unsigned char>();
+  if (pl.use_tc) {
+    // tensor cores; the projected coordinates stay in TMEM unless they are asked for
+    kernels::project_decode_tc(pl.tc, L, p.shift.as<__half>(), p.inv_f.as<float>(), levels,
+                               pl.codes.as<long long>(), pl.dbg.taps ? pl.Y.as<__half>() : nullptr,
+                               pl.tc_error_dev, s);
+    mark();
+  } else {
+    kernels::project_ordered(pl.qh.as<__half>(), p.ldu, p.ut.as<__half>(), p.ldu,
+                             p.shift.as<__half>(), pl.m1, wdt, D, pl.Y.as<__half>(), s);
+    mark();
+    kernels::decode_codes(pl.Y.as<__half>(), int64_t{pl.m1} * p.copies, p.copies, ix.blocks, L,
+                          p.inv_f.as<float>(), levels, pl.codes.as<long long>(), s);
+  }
   mark();
   kernels::probe(pl.codes.as<long long>(), pl.m1, p.copies, L, p.offsets.as<int>(), T1,
                  p.keys.as<long long>(), p.mmax, p.base.as<int>(), p.level_on.as<unsigned char>(),
@@ -223,7 +244,14 @@ auto make_plan(index_impl& ix, search_params const& sp, int m, int k, debug_opti
   pl.qbuf  = alloc<float>(pl, p.device, int64_t{m1} * D, 0);
   pl.qh    = alloc<__half>(pl, p.device, int64_t{m1} * p.ldu);
   pl.qs    = alloc<float>(pl, p.device, int64_t{m1} * sw);
-  pl.Y     = alloc<__half>(pl, p.device, int64_t{m1} * wdt);
+  pl.use_tc = !dbg.ordered_projection && kernels::project_tc_supported(ix.blocks, p.ldu);
+  if (!pl.use_tc || dbg.taps) pl.Y = alloc<__half>(pl, p.device, int64_t{m1} * wdt);
+  if (pl.use_tc) {
+    OCTEX_CUDA_TRY(cudaHostAlloc(reinterpret_cast<void**>(&pl.tc_error_host), sizeof(int), cudaHostAllocMapped));
+    *pl.tc_error_host = 0;
+    OCTEX_CUDA_TRY(cudaHostGetDevicePointer(reinterpret_cast<void**>(&pl.tc_error_dev), pl.tc_error_host, 0));
+    kernels::project_tc_setup(pl.tc, pl.qh.as<__half>(), m1, p.ut.as<__half>(), p.copies, p.ldu);
+  }
   pl.codes = alloc<long long>(pl, p.device, int64_t{m1} * p.copies * L);
   pl.seg   = alloc<int2>(pl, p.device, int64_t{m1} * p.copies);
   pl.si    = alloc<long long>(pl, p.device, int64_t{m1} * pl.KO, 0xff);
@@ -231,7 +259,11 @@ auto make_plan(index_impl& ix, search_params const& sp, int m, int k, debug_opti
   pl.bi    = alloc<long long>(pl, p.device, int64_t{m1} * k);
   pl.bd    = alloc<float>(pl, p.device, int64_t{m1} * k);
   if (sp.waves > 0) pl.done = alloc<int>(pl, p.device, int64_t{m1} * S * sp.waves, 0xff);
-  if (dbg.stats) pl.stats = alloc<long long>(pl, p.device, int64_t{m1} * 8, 0);
+  if (dbg.stats) {
+    pl.stats  = alloc<long long>(pl, p.device, int64_t{m1} * 8, 0);
+    pl.phase1 = alloc<long long>(pl, p.device, int64_t{m1} * 8, 0);
+    pl.phase2 = alloc<long long>(pl, p.device, int64_t{m1} * 8, 0);
+  }
   if (dbg.taps) {
     pl.tap_cap  = p.copies * pl.lr;
     pl.tap_cand = alloc<int>(pl, p.device, int64_t{m1} * pl.tap_cap, 0xff);
@@ -263,6 +295,7 @@ auto make_plan(index_impl& ix, search_params const& sp, int m, int k, debug_opti
   r1.si          = pl.si.as<long long>();
   r1.sd          = pl.sd.as<float>();
   r1.stats       = pl.stats.as<long long>();
+  r1.phase       = pl.phase1.as<long long>();
   if (dbg.taps) {
     r1.tap_cand = pl.tap_cand.as<int>();
     r1.tap_dist = pl.tap_dist.as<float>();
@@ -294,6 +327,7 @@ auto make_plan(index_impl& ix, search_params const& sp, int m, int k, debug_opti
     r2.si          = r1.si;
     r2.sd          = r1.sd;
     r2.stats       = r1.stats;
+    r2.phase       = pl.phase2.as<long long>();
     size_round(pl, r2, S * ix.table_len, S * std::max(sp.waves - 1, 0), p.device);
   }
   kernels::round_allow_smem(pl.smem_max);
@@ -302,6 +336,7 @@ auto make_plan(index_impl& ix, search_params const& sp, int m, int k, debug_opti
   OCTEX_CUDA_TRY(cudaDeviceSynchronize());
   run_batch(ix, pl, p.stream, nullptr);
   OCTEX_CUDA_TRY(cudaStreamSynchronize(p.stream));
+  check_tc(pl);
   cudaGraph_t graph = nullptr;
   OCTEX_CUDA_TRY(cudaStreamBeginCapture(p.stream, cudaStreamCaptureModeThreadLocal));
   try {
@@ -325,7 +360,8 @@ auto get_plan(index_impl& ix, search_params const& sp, int m, int k) -> std::sha
                     "/" + std::to_string(sp.starts) + "/" + std::to_string(sp.waves) + "/" +
                     std::to_string(sp.rerank) + "/" + std::to_string(sp.wave_rerank) + "/" +
                     std::to_string(sp.sketch_rank) + "/" + std::to_string(sp.final_rerank) + "/" +
-                    std::to_string(dbg.stats) + std::to_string(dbg.taps);
+                    std::to_string(dbg.stats) + std::to_string(dbg.taps) +
+                    std::to_string(dbg.ordered_projection);
   std::lock_guard<std::mutex> lock(ix.mu);
   auto it = ix.plans.find(key);
   if (it != ix.plans.end()) return it->second;
@@ -392,6 +428,7 @@ void search_impl(resources const& res,
   OCTEX_CUDA_TRY(cudaStreamWaitEvent(caller, pl->done_ev, 0));
   if (host_out) OCTEX_CUDA_TRY(cudaStreamSynchronize(caller));
   OCTEX_CUDA_TRY(cudaEventDestroy(start));
+  if (host_out) check_tc(*pl);
 }
 
 }  // namespace detail

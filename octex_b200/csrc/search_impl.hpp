@@ -16,8 +16,12 @@ struct plan {
   int device = 0;
   int m = 0, k = 0, KO = 0, lr = 0, R1 = 0, R2 = 0, FR = 0;
   int m1 = 0;  // queries of a batch handled by this process
-  dbuf qbuf, qh, qs, Y, codes, seg, si, sd, done, bi, bd, stats;
+  dbuf qbuf, qh, qs, Y, codes, seg, si, sd, done, bi, bd, stats, phase1, phase2;
   dbuf tap_cand, tap_dist, tap_n, kept1_i, kept1_d;
+  bool use_tc = false;          // tensor-core projection with the decode in its epilogue
+  kernels::project_tc_plan tc;  // its tensor maps
+  int* tc_error_host = nullptr; // pinned, device-visible: non-zero when a wait in that kernel ran out
+  int* tc_error_dev  = nullptr;
   int tap_cap = 0;
   std::vector<dbuf> scratch_cand, scratch_dist;
   kernels::round_args r1, r2;

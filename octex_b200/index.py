@@ -246,6 +246,11 @@ class Index:
     def set_debug(self, stats=False, taps=False):
         _lib.check(_lib.lib().octexB200SetDebug(self._h, C.c_int32(int(stats)), C.c_int32(int(taps))))
 
+    def set_projection(self, ordered=False):
+        """``ordered=True``: project with the kernel that sums in dimension order (a CPU
+        implementation can reproduce its coordinates bit for bit) instead of the tensor cores."""
+        _lib.check(_lib.lib().octexB200SetProjection(self._h, C.c_int32(int(ordered))))
+
     def fetch(self, name: str, dtype, shape=None):
         """A named intermediate array of the last batch as a numpy array."""
         nbytes = C.c_int64(0)

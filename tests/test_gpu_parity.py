@@ -312,3 +312,63 @@ def test_full_size_properties():
     print(f"recall@10 {r:.4f} (read 32, starts 128, waves 3, rerank 256, 24 copies)")
     assert r >= 0.95
     idx.close()
+
+
+def test_tensor_core_projection(oracle, gpu_wide):
+    """The tcgen05 projection against the ordered one on the same operands: fp32 accumulation in a
+    different order, so an fp16 output may land on the neighbouring value (tolerance: one unit in
+    the last place of fp16, on at most 2 % of the coordinates); the cell codes it emits from its
+    own accumulators equal the checker's codes of those same coordinates bit for bit."""
+    idx, arrays, meta, _, queries = gpu_wide
+    nq, C_, L = len(queries), meta["copies"], len(meta["spacings"])
+    kw = dict(read=8, starts=32, waves=1)
+    idx.set_projection(ordered=False)
+    idx.search(queries, 10, **kw)
+    y_tc = idx.fetch("y", np.uint16, (nq, -1))
+    codes_tc = idx.fetch("codes", np.int64, (nq, C_, L))
+    idx.set_projection(ordered=True)
+    idx.search(queries, 10, **kw)
+    y_ord = idx.fetch("y", np.uint16, (nq, -1))
+    idx.set_projection(ordered=False)
+    a, b = y_tc.view(np.float16).astype(np.float32), y_ord.view(np.float16).astype(np.float32)
+    differ = y_tc != y_ord
+    print(f"tensor-core vs ordered projection: {differ.mean():.5f} of the fp16 coordinates differ")
+    assert differ.mean() <= 0.02
+    ulp = np.spacing(np.abs(y_ord.view(np.float16)).astype(np.float16)).astype(np.float32)
+    # one fp16 unit in the last place, plus 3e-5 absolute for coordinates near zero, where the fp32
+    # sums themselves (terms of order 1, 128 of them) differ by more than such a coordinate's ulp
+    worst = float((np.abs(a - b) - ulp).max())
+    print(f"largest |difference| beyond one fp16 ulp: {worst:.3e}")
+    assert (np.abs(a - b) <= ulp + 3e-5).all()
+    _, _, t = oracle.Index(arrays, meta).search(queries, 10, y_in=y_tc, taps=("codes",), **kw)
+    assert np.array_equal(codes_tc, t["codes"])
+
+
+@pytest.mark.parametrize("gen,dim", [("global_descriptor_like", 960), ("embedding_like", 96),
+                                      ("plumbing", 200)])
+def test_other_dimensions(oracle, gen, dim):
+    """The shapes of the other benchmark configurations, small: 960 dimensions (fifteen 64-wide
+    steps of the projection, 1 920-byte rows in the rerank), 96 (operand rows zero-padded to 128)
+    and 200 (not a multiple of 8: the scalar path of the exact distances)."""
+    from octex_b200 import build_index, synth
+    base = getattr(synth, gen)(5000, dim, seed=0)
+    queries = getattr(synth, gen)(150, dim, seed=1)
+    params = small_params(copies=5, blocks=4, pca_dims=64, list_len=16, min_cell=2,
+                          sketch_width=0, table_len=24)
+    arrays, meta = build_index.build_arrays(base, params, device="cpu")
+    idx = octex_b200.attach(arrays, meta, borrow=False)
+    idx.set_debug(stats=True, taps=True)
+    for kw in (dict(read=8, starts=32, waves=2, rerank=64, wave_rerank=64),
+               dict(read=8, starts=48, waves=1, sketch_rank=True, final_rerank=32)):
+        dist, ids, want_dist, want_ids, t, y = check_against_checker(oracle, idx, arrays, meta, queries, **kw)
+        assert np.array_equal(ids, want_ids), (dim, kw)
+        assert np.array_equal(dist.view(np.uint32), want_dist.view(np.uint32)), (dim, kw)
+        assert np.array_equal(idx.fetch("codes", np.int64, t["codes"].shape), t["codes"])
+    # the tensor-core coordinates stay within one fp16 step of the ordered ones
+    idx.set_projection(ordered=True)
+    idx.search(queries, 10, read=8, starts=32, waves=0)
+    y_ord = idx.fetch("y", np.uint16, y.shape).view(np.float16).astype(np.float32)
+    y_tc = y.view(np.float16).astype(np.float32)
+    ulp = np.spacing(np.abs(y_ord).astype(np.float16)).astype(np.float32)
+    assert (np.abs(y_tc - y_ord) <= ulp + 1e-4).all()
+    idx.close()

@@ -184,6 +184,18 @@ OCTEX_B200_EXPORT cuvsError_t octexB200LoadRank(cuvsResources_t res, const char*
                                                 cuvsOctexLoadParams_t params, int32_t rank,
                                                 int32_t world, cuvsOctexIndex_t index);
 
+/* Connect the processes that share an index (world > 1). The reference needs no such step: it
+ * drives all GPUs from one process and reads across them through peer pointers
+ * (cpp/src/neighbors/octex/load.cu:187-202). Here one process calls octexB200CommUniqueId, hands
+ * the 128 bytes to the others by any means (a file, MPI, torch.distributed), and every process
+ * then calls octexB200CommInit with them; the calls return together. Afterwards every process
+ * calls the search with the same queries and parameters and receives all results:
+ * replicate placement answers a slice of each batch per process, shard placement runs the first
+ * round of all rows over the process's copies, exchanges the kept lists (NCCL send / receive),
+ * and runs the waves on the process's slice; an NCCL all-gather brings the slices together. */
+OCTEX_B200_EXPORT cuvsError_t octexB200CommUniqueId(void* id128);
+OCTEX_B200_EXPORT cuvsError_t octexB200CommInit(cuvsOctexIndex_t index, const void* id128);
+
 /* The arrays of an index directory handed over in memory (host or device pointers), with the
  * dtypes and shapes of docs/design.md:27-48. */
 typedef struct {

@@ -90,6 +90,7 @@ SYMBOLS = (
     "cuvsOctexSearch", "octexB200Search", "octexB200LoadRank", "octexB200Attach",
     "octexB200SearchResident", "octexB200ProfileBatch", "octexB200SetDebug", "octexB200Fetch",
     "octexB200CellCodes", "octexB200QueryCodesStatic", "octexB200SetProjection",
+    "octexB200CommUniqueId", "octexB200CommInit",
 )
 
 

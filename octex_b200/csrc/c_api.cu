@@ -432,6 +432,27 @@ cuvsError_t octexB200SetDebug(cuvsOctexIndex_t index, int32_t stats, int32_t tap
   });
 }
 
+cuvsError_t octexB200CommUniqueId(void* id128)
+{
+  return translate([=] {
+    OCTEX_EXPECTS(id128 != nullptr, "octex: a NULL id buffer");
+    octex_b200::detail::communicator::unique_id(id128);
+  });
+}
+
+cuvsError_t octexB200CommInit(cuvsOctexIndex_t index, const void* id128)
+{
+  return translate([=] {
+    OCTEX_EXPECTS(id128 != nullptr, "octex: a NULL id buffer");
+    auto& ix = as_index(*index)->impl();
+    OCTEX_EXPECTS(ix.world > 1, "octex: the index belongs to a single process");
+    std::lock_guard<std::mutex> lock(ix.mu);
+    ix.plans.clear();
+    ix.comm = std::make_unique<octex_b200::detail::communicator>(id128, ix.rank, ix.world,
+                                                                 ix.part.device);
+  });
+}
+
 cuvsError_t octexB200SetProjection(cuvsOctexIndex_t index, int32_t ordered)
 {
   return translate([=] {

@@ -15,6 +15,7 @@
 // * level_on u8 [Cg, L]          1 when the level of the copy holds at least one cell
 #pragma once
 
+#include "comm.hpp"
 #include "common.hpp"
 
 #include <octex_b200.hpp>
@@ -78,6 +79,7 @@ struct index_impl {
   std::mutex mu;  // guards plans
   std::map<std::string, std::shared_ptr<plan>> plans;
   debug_options debug;
+  std::unique_ptr<communicator> comm;  // set when world > 1 (octexB200CommInit)
   ~index_impl();
 };
 

@@ -138,10 +138,41 @@ void run_batch(index_impl const& ix, plan& pl, cudaStream_t s, std::vector<cudaE
   mark();
   kernels::round_lists(pl.r1, s);
   mark();
-  if (pl.dbg.taps) {
-    OCTEX_CUDA_TRY(cudaMemcpyAsync(pl.kept1_i.ptr, pl.si.ptr, pl.kept1_i.size, cudaMemcpyDeviceToDevice, s));
-    OCTEX_CUDA_TRY(cudaMemcpyAsync(pl.kept1_d.ptr, pl.sd.ptr, pl.kept1_d.size, cudaMemcpyDeviceToDevice, s));
+  if (pl.shard) {
+    // Every process ran the first round of all m rows over its own copies. Row block [lo_r, hi_r)
+    // of each kept list goes to process r (search_kernels.cuh:517-539 reads the same blocks through
+    // peer pointers); then the nearest copy of every id, best KO (merge_kept_kernel).
+    auto& c        = *ix.comm;
+    const size_t e = static_cast<size_t>(pl.KO);
+    c.group_start();
+    for (int r = 0; r < pl.world; r++) {
+      const int lo_r = static_cast<int>(int64_t{pl.m} * r / pl.world);
+      const int hi_r = static_cast<int>(int64_t{pl.m} * (r + 1) / pl.world);
+      long long* ri  = pl.recv_i.as<long long>() + static_cast<size_t>(r) * pl.mwmax * e;
+      float* rd      = pl.recv_d.as<float>() + static_cast<size_t>(r) * pl.mwmax * e;
+      if (r == pl.rank) {
+        OCTEX_CUDA_TRY(cudaMemcpyAsync(ri, pl.si.as<long long>() + pl.lo * e, pl.mw * e * sizeof(long long),
+                                       cudaMemcpyDeviceToDevice, s));
+        OCTEX_CUDA_TRY(cudaMemcpyAsync(rd, pl.sd.as<float>() + pl.lo * e, pl.mw * e * sizeof(float),
+                                       cudaMemcpyDeviceToDevice, s));
+        continue;
+      }
+      c.send(pl.si.as<long long>() + lo_r * e, (hi_r - lo_r) * e * sizeof(long long), r, s);
+      c.send(pl.sd.as<float>() + lo_r * e, (hi_r - lo_r) * e * sizeof(float), r, s);
+      c.recv(ri, pl.mw * e * sizeof(long long), r, s);
+      c.recv(rd, pl.mw * e * sizeof(float), r, s);
+    }
+    c.group_end();
+    kernels::merge_kept(pl.recv_i.as<long long>(), pl.recv_d.as<float>(), pl.world,
+                        int64_t{pl.mwmax} * pl.KO, pl.KO, pl.P_merge, pl.mw, pl.wsi, pl.wsd, s);
   }
+  if (pl.dbg.taps && pl.mw > 0) {
+    OCTEX_CUDA_TRY(cudaMemcpyAsync(pl.kept1_i.ptr, pl.wsi, sizeof(long long) * pl.mw * pl.KO,
+                                   cudaMemcpyDeviceToDevice, s));
+    OCTEX_CUDA_TRY(cudaMemcpyAsync(pl.kept1_d.ptr, pl.wsd, sizeof(float) * pl.mw * pl.KO,
+                                   cudaMemcpyDeviceToDevice, s));
+  }
+  const float* Qw = pl.qbuf.as<float>() + static_cast<size_t>(pl.lo - pl.q1) * D;
   for (int wv = 0; wv < pl.sp.waves; wv++) {
     kernels::round_args r = pl.r2;
     r.done_off            = wv * pl.sp.starts;
@@ -149,14 +180,18 @@ void run_batch(index_impl const& ix, plan& pl, cudaStream_t s, std::vector<cudaE
     mark();
   }
   if (pl.sp.sketch_rank && pl.FR > 0) {
-    kernels::final_rerank(pl.si.as<long long>(), pl.KO, pl.FR, p.vectors.as<__half>(), D,
-                          pl.qbuf.as<float>(), pl.k, pl.m1, pl.bi.as<long long>(), pl.bd.as<float>(),
-                          pl.stats.as<long long>(), s);
+    kernels::final_rerank(pl.wsi, pl.KO, pl.FR, p.vectors.as<__half>(), D, Qw, pl.k, pl.mw,
+                          pl.bi.as<long long>(), pl.bd.as<float>(), pl.stats.as<long long>(), s);
   } else {
-    kernels::take_k(pl.si.as<long long>(), pl.sd.as<float>(), pl.KO, pl.k, pl.m1,
-                    pl.bi.as<long long>(), pl.bd.as<float>(), s);
+    kernels::take_k(pl.wsi, pl.wsd, pl.KO, pl.k, pl.mw, pl.bi.as<long long>(), pl.bd.as<float>(), s);
   }
   mark();
+  if (pl.world > 1) {
+    // every process gets the results of all slices (blocks of mwmax rows, the last rows of a
+    // block unused when the slices differ in size)
+    ix.comm->all_gather(pl.bi.ptr, pl.gi.ptr, sizeof(long long) * pl.mwmax * pl.k, s);
+    ix.comm->all_gather(pl.bd.ptr, pl.gd.ptr, sizeof(float) * pl.mwmax * pl.k, s);
+  }
   OCTEX_CUDA_TRY(cudaPeekAtLastError());
 }
 
@@ -235,8 +270,20 @@ auto make_plan(index_impl& ix, search_params const& sp, int m, int k, debug_opti
                 "octex: copies x read too large for the shared-memory hash set");
   OCTEX_EXPECTS(sp.waves == 0 || int64_t{S} * ix.table_len <= kernels::kMaxHash,
                 "octex: starts x table_len too large for the shared-memory hash set");
-  OCTEX_EXPECTS(ix.world == 1, "octex: this plan serves a single process");
-  pl.m1 = m;
+  // slices (search.cu:666-676 of the reference)
+  pl.rank  = ix.rank;
+  pl.world = ix.world;
+  pl.shard = ix.params.mode == placement::shard && ix.world > 1;
+  OCTEX_EXPECTS(ix.world == 1 || ix.comm != nullptr,
+                "octex: an index shared by several processes needs its communicator first "
+                "(octexB200CommInit)");
+  OCTEX_EXPECTS(!pl.shard || ix.world * pl.KO <= 4096, "octex: devices * max(starts, k) <= 4096");
+  pl.lo    = static_cast<int>(int64_t{m} * ix.rank / ix.world);
+  pl.hi    = static_cast<int>(int64_t{m} * (ix.rank + 1) / ix.world);
+  pl.mw    = pl.hi - pl.lo;
+  pl.mwmax = (m + ix.world - 1) / ix.world;
+  pl.q1    = pl.shard ? 0 : pl.lo;
+  pl.m1    = pl.shard ? m : pl.mw;
 
   OCTEX_CUDA_TRY(cudaSetDevice(p.device));
   const int m1  = std::max(pl.m1, 1);
@@ -256,8 +303,26 @@ auto make_plan(index_impl& ix, search_params const& sp, int m, int k, debug_opti
   pl.seg   = alloc<int2>(pl, p.device, int64_t{m1} * p.copies);
   pl.si    = alloc<long long>(pl, p.device, int64_t{m1} * pl.KO, 0xff);
   pl.sd    = alloc<float>(pl, p.device, int64_t{m1} * pl.KO);
-  pl.bi    = alloc<long long>(pl, p.device, int64_t{m1} * k);
-  pl.bd    = alloc<float>(pl, p.device, int64_t{m1} * k);
+  const int mwmax = std::max(pl.mwmax, 1);
+  pl.bi    = alloc<long long>(pl, p.device, int64_t{mwmax} * k, 0xff);
+  pl.bd    = alloc<float>(pl, p.device, int64_t{mwmax} * k, 0);
+  pl.wsi   = pl.si.as<long long>();
+  pl.wsd   = pl.sd.as<float>();
+  if (pl.shard) {
+    pl.si2    = alloc<long long>(pl, p.device, int64_t{mwmax} * pl.KO, 0xff);
+    pl.sd2    = alloc<float>(pl, p.device, int64_t{mwmax} * pl.KO);
+    pl.recv_i = alloc<long long>(pl, p.device, int64_t{ix.world} * mwmax * pl.KO, 0xff);
+    pl.recv_d = alloc<float>(pl, p.device, int64_t{ix.world} * mwmax * pl.KO, 0);
+    pl.wsi    = pl.si2.as<long long>();
+    pl.wsd    = pl.sd2.as<float>();
+    pl.P_merge = 2;
+    while (pl.P_merge < ix.world * pl.KO)
+      pl.P_merge <<= 1;
+  }
+  if (ix.world > 1) {
+    pl.gi = alloc<long long>(pl, p.device, int64_t{ix.world} * mwmax * k, 0xff);
+    pl.gd = alloc<float>(pl, p.device, int64_t{ix.world} * mwmax * k, 0);
+  }
   if (sp.waves > 0) pl.done = alloc<int>(pl, p.device, int64_t{m1} * S * sp.waves, 0xff);
   if (dbg.stats) {
     pl.stats  = alloc<long long>(pl, p.device, int64_t{m1} * 8, 0);
@@ -307,7 +372,7 @@ auto make_plan(index_impl& ix, search_params const& sp, int m, int k, debug_opti
   if (sp.waves > 0) {
     auto& r2       = pl.r2;
     r2             = kernels::round_args{};
-    r2.m           = pl.m1;
+    r2.m           = pl.mw;
     r2.nseg        = S;
     r2.table       = p.table.as<int>();
     r2.table_len   = ix.table_len;
@@ -315,17 +380,17 @@ auto make_plan(index_impl& ix, search_params const& sp, int m, int k, debug_opti
     r2.done_stride = S * sp.waves;
     r2.sketch      = r1.sketch;
     r2.scale       = r1.scale;
-    r2.qs          = r1.qs;
+    r2.qs          = r1.qs + static_cast<size_t>(pl.lo - pl.q1) * sw;
     r2.sw          = sw;
     r2.vectors     = r1.vectors;
     r2.D           = D;
-    r2.Q           = r1.Q;
+    r2.Q           = r1.Q + static_cast<size_t>(pl.lo - pl.q1) * D;
     r2.R           = pl.R2;
     r2.KO          = pl.KO;
     r2.sketch_rank = r1.sketch_rank;
     r2.fresh       = 0;
-    r2.si          = r1.si;
-    r2.sd          = r1.sd;
+    r2.si          = pl.wsi;
+    r2.sd          = pl.wsd;
     r2.stats       = r1.stats;
     r2.phase       = pl.phase2.as<long long>();
     size_round(pl, r2, S * ix.table_len, S * std::max(sp.waves - 1, 0), p.device);
@@ -337,6 +402,10 @@ auto make_plan(index_impl& ix, search_params const& sp, int m, int k, debug_opti
   run_batch(ix, pl, p.stream, nullptr);
   OCTEX_CUDA_TRY(cudaStreamSynchronize(p.stream));
   check_tc(pl);
+  OCTEX_CUDA_TRY(cudaEventCreateWithFlags(&pl.done_ev, cudaEventDisableTiming));
+  // batches that exchange data between processes are launched kernel by kernel (the NCCL calls
+  // sit between the kernels); a single process replays one graph per batch
+  if (ix.world > 1) return plp;
   cudaGraph_t graph = nullptr;
   OCTEX_CUDA_TRY(cudaStreamBeginCapture(p.stream, cudaStreamCaptureModeThreadLocal));
   try {
@@ -349,7 +418,6 @@ auto make_plan(index_impl& ix, search_params const& sp, int m, int k, debug_opti
   OCTEX_CUDA_TRY(cudaStreamEndCapture(p.stream, &graph));
   OCTEX_CUDA_TRY(cudaGraphInstantiate(&pl.graph, graph, 0));
   OCTEX_CUDA_TRY(cudaGraphDestroy(graph));
-  OCTEX_CUDA_TRY(cudaEventCreateWithFlags(&pl.done_ev, cudaEventDisableTiming));
   return plp;
 }
 
@@ -408,19 +476,41 @@ void search_impl(resources const& res,
   for (int64_t b0 = 0; b0 < nq; b0 += m) {
     const int n = static_cast<int>(std::min<int64_t>(m, nq - b0));
     if (!resident) {
-      OCTEX_CUDA_TRY(cudaMemcpyAsync(pl->qbuf.ptr, queries + b0 * D, sizeof(float) * n * D,
-                                     cudaMemcpyDefault, s));
-      if (n < pl->m1) kernels::pad_rows(pl->qbuf.as<float>(), n, pl->m1, D, s);  // search.cu:870-883
+      // rows [q1, q1 + m1) of the batch, the part beyond its end filled with copies of a row
+      // (search.cu:870-883)
+      int have = std::clamp(n - pl->q1, 0, pl->m1);
+      if (have > 0) {
+        OCTEX_CUDA_TRY(cudaMemcpyAsync(pl->qbuf.ptr, queries + (b0 + pl->q1) * D,
+                                       sizeof(float) * have * D, cudaMemcpyDefault, s));
+      } else if (pl->m1 > 0) {
+        OCTEX_CUDA_TRY(cudaMemcpyAsync(pl->qbuf.ptr, queries + b0 * D, sizeof(float) * D,
+                                       cudaMemcpyDefault, s));
+        have = 1;
+      }
+      if (have < pl->m1) kernels::pad_rows(pl->qbuf.as<float>(), have, pl->m1, D, s);
     }
-    if (sp.use_graph)
+    if (sp.use_graph && pl->graph != nullptr)
       OCTEX_CUDA_TRY(cudaGraphLaunch(pl->graph, s));
     else
-      run_batch(ix, *pl, s, nullptr);  // search_params::use_graph = false: direct launches
-    if (!resident) {
+      run_batch(ix, *pl, s, nullptr);  // use_graph = false, or a batch with exchanges
+    if (!resident && pl->world == 1) {
       OCTEX_CUDA_TRY(cudaMemcpyAsync(neighbors + b0 * k, pl->bi.ptr, sizeof(int64_t) * n * k,
                                      cudaMemcpyDefault, s));
       OCTEX_CUDA_TRY(cudaMemcpyAsync(distances + b0 * k, pl->bd.ptr, sizeof(float) * n * k,
                                      cudaMemcpyDefault, s));
+    } else if (!resident) {
+      // the gathered results: block r holds the rows [lo_r, hi_r) of the batch
+      for (int r = 0; r < pl->world; r++) {
+        const int lo_r = static_cast<int>(int64_t{m} * r / pl->world);
+        const int hi_r = static_cast<int>(int64_t{m} * (r + 1) / pl->world);
+        const int rows = std::clamp(n - lo_r, 0, hi_r - lo_r);
+        if (rows == 0) continue;
+        const size_t at = static_cast<size_t>(r) * pl->mwmax * k;
+        OCTEX_CUDA_TRY(cudaMemcpyAsync(neighbors + (b0 + lo_r) * k, pl->gi.as<long long>() + at,
+                                       sizeof(int64_t) * rows * k, cudaMemcpyDefault, s));
+        OCTEX_CUDA_TRY(cudaMemcpyAsync(distances + (b0 + lo_r) * k, pl->gd.as<float>() + at,
+                                       sizeof(float) * rows * k, cudaMemcpyDefault, s));
+      }
     }
   }
   OCTEX_CUDA_TRY(cudaEventRecord(pl->done_ev, s));

@@ -15,7 +15,19 @@ struct plan {
   debug_options dbg;
   int device = 0;
   int m = 0, k = 0, KO = 0, lr = 0, R1 = 0, R2 = 0, FR = 0;
-  int m1 = 0;  // queries of a batch handled by this process
+  // Who answers what in a batch of m rows when `world` processes share the index
+  // (search.cu:666-676 of the reference, per GPU there, per process here): the first round runs on
+  // rows [q1, q1 + m1) — all m rows when the copies are sharded, the own slice otherwise — and the
+  // waves on the own slice [lo, hi).
+  int rank = 0, world = 1;
+  bool shard = false;
+  int m1 = 0, q1 = 0, lo = 0, hi = 0, mw = 0, mwmax = 0;
+  dbuf si2, sd2;        // shard: kept list of the own slice after the cross-process merge
+  dbuf recv_i, recv_d;  // shard: [world, mwmax, KO] first-round kept lists of every process
+  dbuf gi, gd;          // world > 1: [world, mwmax, k] results of every process
+  long long* wsi = nullptr;  // kept list the waves work on [mw, KO]
+  float* wsd     = nullptr;
+  int P_merge    = 0;   // keys sorted by the cross-process merge (power of two >= world * KO)
   dbuf qbuf, qh, qs, Y, codes, seg, si, sd, done, bi, bd, stats, phase1, phase2;
   dbuf tap_cand, tap_dist, tap_n, kept1_i, kept1_d;
   bool use_tc = false;          // tensor-core projection with the decode in its epilogue

@@ -35,33 +35,48 @@ __global__ void pad_rows_kernel(float* __restrict__ q, int from, int m, int D)
 }
 
 // Centre (search_kernels.cuh:57-69) fused with the sketch-space projection of the query
-// (search.cu:321-341): one block per query, the centred query in shared memory, thread s owns
-// sketch coordinate s.
-__global__ void center_sketch_kernel(const float* __restrict__ q,
-                                     const float* __restrict__ mean,
-                                     const float* __restrict__ basis,
-                                     int D,
-                                     int S,
-                                     __half* __restrict__ qh,
-                                     int ldq,
-                                     float* __restrict__ qs)
+// (search.cu:321-341): a block takes kCenterRows queries, their centred copies sit in shared
+// memory, thread s owns sketch coordinate s of all of them, so every element of the basis is read
+// once per block; each (query, coordinate) sum runs over the dimensions in order.
+constexpr int kCenterRows = 8;
+__global__ void __launch_bounds__(128) center_sketch_kernel(const float* __restrict__ q,
+                                                            const float* __restrict__ mean,
+                                                            const float* __restrict__ basis,
+                                                            int m,
+                                                            int D,
+                                                            int S,
+                                                            __half* __restrict__ qh,
+                                                            int ldq,
+                                                            float* __restrict__ qs)
 {
-  extern __shared__ float qc[];
-  const int row = blockIdx.x;
-  for (int d = threadIdx.x; d < ldq; d += blockDim.x) {
+  extern __shared__ float qc[];  // [kCenterRows][D]
+  const int row0 = blockIdx.x * kCenterRows;
+  const int rows = min(kCenterRows, m - row0);
+  for (int i = threadIdx.x; i < rows * ldq; i += blockDim.x) {
+    const int r = i / ldq, d = i - r * ldq;
     float v = 0.f;
     if (d < D) {
-      v     = __fsub_rn(q[static_cast<int64_t>(row) * D + d], mean[d]);
-      qc[d] = v;
+      v             = __fsub_rn(q[static_cast<int64_t>(row0 + r) * D + d], mean[d]);
+      qc[r * D + d] = v;
     }
-    qh[static_cast<int64_t>(row) * ldq + d] = __float2half_rn(v);
+    qh[static_cast<int64_t>(row0 + r) * ldq + d] = __float2half_rn(v);
   }
+  for (int i = rows * D + threadIdx.x; i < kCenterRows * D; i += blockDim.x)
+    qc[i] = 0.f;
   __syncthreads();
   for (int s = threadIdx.x; s < S; s += blockDim.x) {
-    float acc = 0.f;
-    for (int d = 0; d < D; d++)
-      acc = __fmaf_rn(qc[d], basis[static_cast<int64_t>(d) * S + s], acc);
-    qs[static_cast<int64_t>(row) * S + s] = acc;
+    float acc[kCenterRows];
+#pragma unroll
+    for (int r = 0; r < kCenterRows; r++)
+      acc[r] = 0.f;
+    for (int d = 0; d < D; d++) {
+      const float b = basis[static_cast<int64_t>(d) * S + s];
+#pragma unroll
+      for (int r = 0; r < kCenterRows; r++)
+        acc[r] = __fmaf_rn(qc[r * D + d], b, acc[r]);
+    }
+    for (int r = 0; r < rows; r++)
+      qs[static_cast<int64_t>(row0 + r) * S + s] = acc[r];
   }
 }
 
@@ -264,7 +279,14 @@ void center_sketch(const float* q, const float* mean, const float* basis, int m,
                    __half* qh, int ldq, float* qs, cudaStream_t s)
 {
   if (m <= 0) return;
-  center_sketch_kernel<<<m, 128, sizeof(float) * D, s>>>(q, mean, basis, D, S, qh, ldq, qs);
+  const size_t smem = sizeof(float) * kCenterRows * D;
+  static size_t allowed = 48 << 10;
+  if (smem > allowed) {
+    cudaFuncSetAttribute(center_sketch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    allowed = smem;
+  }
+  center_sketch_kernel<<<(m + kCenterRows - 1) / kCenterRows, 128, smem, s>>>(q, mean, basis, m, D, S, qh,
+                                                                             ldq, qs);
 }
 
 void project_ordered(const __half* qh, int ldq, const __half* ut, int ldu, const __half* shift,

@@ -10,7 +10,7 @@
 // copy from TMEM (tcgen05.ld 32x32b.x32 hands a lane exactly one copy), rounds them to fp16 and
 // decodes every populated spacing.
 //
-// One 128 x 128 output tile per block of 128 threads. Operand tiles of 128 rows x 64 halves
+// One 128 x 128 output tile per block of 256 threads. Operand tiles of 128 rows x 64 halves
 // (128 bytes, the swizzle span) come in by TMA (cp.async.bulk.tensor, no cluster forms) into a
 // two-stage ring; one thread issues the copies and the MMAs; every wait on an mbarrier is bounded
 // and a wait that runs out sets an error word, lets the block free its TMEM and return.
@@ -33,7 +33,7 @@ constexpr int kTileM    = 128;  // queries per tile = TMEM lanes
 constexpr int kTileN    = 128;  // projected coordinates per tile = 4 copies of 32
 constexpr int kTileK    = 64;   // halves per operand row in a stage (128 bytes)
 constexpr int kStages   = 2;
-constexpr int kThreads  = 128;
+constexpr int kThreads  = 256;  // two warps per TMEM lane quarter, each decoding half of the copies
 constexpr int kTmemCols = 128;  // fp32 accumulator columns
 constexpr uint32_t kStageBytes = (kTileM + kTileN) * kTileK * 2;
 constexpr uint32_t kSpinLimit  = 1u << 21;  // polls of an mbarrier before giving up
@@ -127,7 +127,7 @@ struct __align__(1024) tc_smem {
   float inv_f[16];
 };
 
-__global__ void __launch_bounds__(kThreads) project_decode_tc_kernel(
+__global__ void __launch_bounds__(kThreads, 3) project_decode_tc_kernel(
   const __grid_constant__ CUtensorMap map_a,
   const __grid_constant__ CUtensorMap map_b,
   int m,
@@ -216,11 +216,15 @@ __global__ void __launch_bounds__(kThreads) project_decode_tc_kernel(
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   __syncwarp();
 
-  const int row = tile_m * kTileM + warp * 32 + lane;
-  for (int cc = 0; cc < kTileN / 32; cc++) {
+  // warp w reads TMEM lanes 32 (w % 4) .. + 31; warps 0-3 take the first half of the tile's copies,
+  // warps 4-7 the second
+  const int quarter = warp & 3;
+  const int row     = tile_m * kTileM + quarter * 32 + lane;
+  constexpr int kHalf = kTileN / 32 / 2;
+  for (int cc = (warp >> 2) * kHalf; cc < (warp >> 2) * kHalf + kHalf; cc++) {
     __syncwarp();  // the TMEM load below is a warp-wide instruction
     uint32_t r[32];
-    const uint32_t taddr = tmem + (static_cast<uint32_t>(warp * 32) << 16) + static_cast<uint32_t>(cc * 32);
+    const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(cc * 32);
     asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
       "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "

@@ -41,7 +41,7 @@ struct round_layout {
     cand   = take(in_smem);
     dist   = take(in_smem);
     pool   = take(2 * (a.KO + rm));
-    sorted = take(2 * a.P);
+    sorted = take(4 * a.P);
     sid    = take(rm);
     sdv    = take(rm);
     qv     = take(a.sw);
@@ -190,92 +190,113 @@ __device__ __forceinline__ radix_cut_t radix_cut(KeyAt key_at, int n, int R, uns
   return c;
 }
 
-/// Sixteen int8 codes against sixteen (scale, query) pairs: sum of (code * scale - q)^2 with two
-/// fused multiply-adds per code, in code order. The int8 -> float conversion goes through the
-/// mantissa of 2^23 (exact for every int8 value), which keeps it off the conversion pipe.
-__device__ __forceinline__ float sketch_chunk(const int4& w, const float* __restrict__ sc,
-                                              const float* __restrict__ qv)
+/// Eight int8 codes (two 32-bit words) against eight (scale, query) pairs: sum of
+/// (code * scale - q)^2 with two fused multiply-adds per code, in code order. The int8 -> float
+/// conversion goes through the mantissa of 2^23 (exact for every int8 value), which keeps it off
+/// the conversion pipe.
+__device__ __forceinline__ float sketch_chunk8(uint2 w, const float* s, const float* q)
 {
-  const unsigned* u = reinterpret_cast<const unsigned*>(&w);
+  const unsigned x0 = w.x ^ 0x80808080u, x1 = w.y ^ 0x80808080u;  // code + 128 in every byte
   float d           = 0.f;
 #pragma unroll
-  for (int wd = 0; wd < 4; wd++) {
-    const unsigned x = u[wd] ^ 0x80808080u;  // code + 128 in every byte
-    const float4 s4  = *reinterpret_cast<const float4*>(sc + 4 * wd);
-    const float4 q4  = *reinterpret_cast<const float4*>(qv + 4 * wd);
-    const float s[4] = {s4.x, s4.y, s4.z, s4.w};
-    const float q[4] = {q4.x, q4.y, q4.z, q4.w};
-#pragma unroll
-    for (int b = 0; b < 4; b++) {
-      const float code =
-        __fadd_rn(__uint_as_float(__byte_perm(x, 0x4B000000u, 0x7650 + b)), -8388736.0f);
-      const float t = __fmaf_rn(code, s[b], -q[b]);
-      d             = __fmaf_rn(t, t, d);
-    }
+  for (int b = 0; b < 8; b++) {
+    const float code =
+      __fadd_rn(__uint_as_float(__byte_perm(b < 4 ? x0 : x1, 0x4B000000u, 0x7650 + (b & 3))), -8388736.0f);
+    const float t = __fmaf_rn(code, s[b], -q[b]);
+    d             = __fmaf_rn(t, t, d);
   }
   return d;
 }
 
+/// Rows j and j + stride of a lane group: squared distances of two fp16 rows to the query.
+/// kRegs: the row has at most two 16-byte steps per lane (D <= 128) and the lane's query
+/// coordinates qr[16] live in registers; otherwise they are read from shared memory (fq).
+template <bool kRegs>
+__device__ __forceinline__ void exact_pair(const uint4* const (&row)[2], int D, int sub, const float* fq,
+                                           const float (&qr)[16], float (&out)[2])
+{
+  float acc[2][4];
+#pragma unroll
+  for (int u = 0; u < 2; u++)
+#pragma unroll
+    for (int t = 0; t < 4; t++)
+      acc[u][t] = 0.f;
+  // two 16-byte steps of both rows are loaded before any of them is used
+  for (int h0 = 8 * sub; h0 < D; h0 += 128) {
+    uint4 v[2][2];
+#pragma unroll
+    for (int s = 0; s < 2; s++)
+#pragma unroll
+      for (int u = 0; u < 2; u++)
+        if (row[u] != nullptr && h0 + 64 * s < D) v[s][u] = __ldg(row[u] + ((h0 + 64 * s) >> 3));
+#pragma unroll
+    for (int s = 0; s < 2; s++) {
+      const int hs = h0 + 64 * s;
+      if (hs >= D) break;
+#pragma unroll
+      for (int u = 0; u < 2; u++) {
+        if (row[u] == nullptr) continue;
+        const __half2* h2 = reinterpret_cast<const __half2*>(&v[s][u]);
+#pragma unroll
+        for (int t = 0; t < 4; t++) {
+          const float2 x = __half22float2(h2[t]);
+          const float qa = kRegs ? qr[8 * s + 2 * t] : fq[hs + 2 * t];
+          const float qb = kRegs ? qr[8 * s + 2 * t + 1] : fq[hs + 2 * t + 1];
+          const float a  = __fsub_rn(x.x, qa);
+          const float b  = __fsub_rn(x.y, qb);
+          acc[u][t]      = __fmaf_rn(b, b, __fmaf_rn(a, a, acc[u][t]));
+        }
+      }
+    }
+    if (kRegs) break;
+  }
+  // butterfly over the 32 partial sums, strides 1, 2 (inside the lane), then 4, 8, 16 (lanes)
+#pragma unroll
+  for (int u = 0; u < 2; u++) {
+    float v = __fadd_rn(__fadd_rn(acc[u][0], acc[u][1]), __fadd_rn(acc[u][2], acc[u][3]));
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1)
+      v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, o));
+    out[u] = v;
+  }
+}
+
 /// Squared distances of the fp16 rows sid[0, ns) (entries < 0 are skipped) to the fp32 query fq,
 /// written over sdv. Summation order (shared with the CPU checker): element pair k feeds partial
-/// sum k mod 32 with two fused multiply-adds; a butterfly over the 32 partial sums
-/// (search_kernels.cuh:325-342 is the reference's warp-per-row form of the same sum). Eight lanes
-/// own a row, each reading 16 bytes per step; a warp works on eight rows at a time.
+/// sum k mod 32 with two fused multiply-adds; a butterfly over the 32 partial sums with strides
+/// 1, 2, 4, 8, 16 (search_kernels.cuh:325-342 is the reference's warp-per-row form of the same
+/// sum). Eight lanes own a row, each reading 16 bytes per step (partial sums 4 lane .. 4 lane + 3);
+/// a warp works on eight rows at a time.
 __device__ __forceinline__ void exact_distances(
   const int* sid, int ns, const __half* __restrict__ vectors, int D, const float* fq, float* sdv)
 {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   if ((D & 7) == 0) {
     const int sub = lane & 7, grp = lane >> 3;
+    const bool regs = D <= 128;
+    float qr[16];
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+      const int h = 8 * sub + 64 * (i >> 3) + (i & 7);
+      qr[i]       = (regs && h < D) ? fq[h] : 0.f;
+    }
     for (int jb = 0; jb < ns; jb += nw * 8) {
       int j[2];
       const uint4* row[2];
-      float acc[2][4];
 #pragma unroll
       for (int u = 0; u < 2; u++) {
         j[u]         = jb + u * nw * 4 + warp * 4 + grp;
         const int id = j[u] < ns ? sid[j[u]] : -1;
         row[u] = id >= 0 ? reinterpret_cast<const uint4*>(vectors + static_cast<int64_t>(id) * D) : nullptr;
-#pragma unroll
-        for (int t = 0; t < 4; t++)
-          acc[u][t] = 0.f;
       }
-      // two 16-byte steps of both rows are loaded before any of them is used
-      for (int h0 = 8 * sub; h0 < D; h0 += 128) {
-        uint4 v[2][2];
+      float out[2];
+      if (regs)
+        exact_pair<true>(row, D, sub, fq, qr, out);
+      else
+        exact_pair<false>(row, D, sub, fq, qr, out);
 #pragma unroll
-        for (int s = 0; s < 2; s++)
-#pragma unroll
-          for (int u = 0; u < 2; u++)
-            if (row[u] != nullptr && h0 + 64 * s < D) v[s][u] = __ldg(row[u] + ((h0 + 64 * s) >> 3));
-#pragma unroll
-        for (int s = 0; s < 2; s++) {
-          const int hs = h0 + 64 * s;
-          if (hs >= D) break;
-#pragma unroll
-          for (int u = 0; u < 2; u++) {
-            if (row[u] == nullptr) continue;
-            const __half2* h2 = reinterpret_cast<const __half2*>(&v[s][u]);
-#pragma unroll
-            for (int t = 0; t < 4; t++) {
-              const float2 x = __half22float2(h2[t]);
-              const float a  = __fsub_rn(x.x, fq[hs + 2 * t]);
-              const float b  = __fsub_rn(x.y, fq[hs + 2 * t + 1]);
-              acc[u][t]      = __fmaf_rn(b, b, __fmaf_rn(a, a, acc[u][t]));
-            }
-          }
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < 2; u++) {
-#pragma unroll
-        for (int o = 4; o; o >>= 1)
-#pragma unroll
-          for (int t = 0; t < 4; t++)
-            acc[u][t] = __fadd_rn(acc[u][t], __shfl_xor_sync(0xffffffffu, acc[u][t], o));
-        if (row[u] != nullptr && sub == 0)
-          sdv[j[u]] = __fadd_rn(__fadd_rn(acc[u][0], acc[u][2]), __fadd_rn(acc[u][1], acc[u][3]));
-      }
+      for (int u = 0; u < 2; u++)
+        if (row[u] != nullptr && sub == 0) sdv[j[u]] = out[u];
     }
   } else {
     for (int j = warp; j < ns; j += nw) {
@@ -289,7 +310,7 @@ __device__ __forceinline__ void exact_distances(
         acc            = __fmaf_rn(b, b, __fmaf_rn(a, a, acc));
       }
 #pragma unroll
-      for (int o = 16; o; o >>= 1)
+      for (int o = 1; o < 32; o <<= 1)
         acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, o));
       if (lane == 0) sdv[j] = acc;
     }
@@ -298,10 +319,13 @@ __device__ __forceinline__ void exact_distances(
 }
 
 /// Merge the new (distance, id) pairs sid / sdv [0, ns) (entries with sid < 0 are skipped; no id is
-/// in the kept list already) into the kept list pb / pd of KO: the KO smallest keys, ascending,
-/// padded with (-1, +inf). Same result as sorting kept + new and taking the first KO distinct keys
-/// (search_kernels.cuh:372-415); here the KO smallest are cut out by radix passes and only they are
-/// sorted. pool holds KO + ns keys, sorted holds P (power of two >= KO).
+/// in the kept list already) into the kept list of KO: the KO smallest keys, ascending, padded
+/// with (-1, +inf), written to pb / pd. Same result as sorting kept + new and taking the first KO
+/// distinct keys (search_kernels.cuh:372-415). A new key beyond the last entry of a full kept list
+/// cannot make it and is dropped at once; what remains is sorted directly when it is short, or the
+/// KO smallest are cut out by radix passes first. kid / kd: the kept list as it was (shared
+/// memory), null when it starts empty. pool holds KO + ns keys, sorted holds 2 * P (P a power of
+/// two >= KO).
 __device__ __forceinline__ void merge_into_kept(unsigned long long* pool,
                                                 unsigned long long* sorted,
                                                 int P,
@@ -316,52 +340,57 @@ __device__ __forceinline__ void merge_into_kept(unsigned long long* pool,
                                                 unsigned* hist,
                                                 int* ctrl)
 {
-  // kid / kd: the kept list as it was (shared memory), null when it starts empty
   const bool fresh = kid == nullptr;
   if (threadIdx.x == 0) ctrl[6] = 0;
-  __syncthreads();
-  // the kept list is packed (valid entries first), new keys are appended behind KO in any order
-  for (int i = threadIdx.x; i < KO; i += blockDim.x)
-    pool[i] = (!fresh && kid[i] >= 0) ? rank_key(kd[i], static_cast<unsigned>(kid[i])) : kNoKey;
-  for (int i = threadIdx.x; i < ns; i += blockDim.x)
-    if (sid[i] >= 0) pool[KO + atomicAdd(&ctrl[6], 1)] = rank_key(sdv[i], static_cast<unsigned>(sid[i]));
-  __syncthreads();
-  const int nn = ctrl[6];
-  int nk       = 0;
-  if (!fresh) {  // number of valid kept entries: first index holding no key
+  // the kept list is packed (valid entries first): nk = first index without an id
+  int nk = 0;
+  if (!fresh) {
     int lo = 0, hi = KO;
     while (lo < hi) {
       const int mid = (lo + hi) >> 1;
-      if (pool[mid] != kNoKey)
+      if (kid[mid] >= 0)
         lo = mid + 1;
       else
         hi = mid;
     }
     nk = lo;
   }
-  const int total = nk + nn;
-  auto key_at     = [&](int i) { return i < nk ? pool[i] : pool[KO + (i - nk)]; };
-  int cnt         = total;
-  if (total > KO) {
+  const unsigned long long bound =
+    nk == KO && KO > 0 ? rank_key(kd[KO - 1], static_cast<unsigned>(kid[KO - 1])) : kNoKey;
+  __syncthreads();
+  for (int i = threadIdx.x; i < nk; i += blockDim.x)
+    pool[i] = rank_key(kd[i], static_cast<unsigned>(kid[i]));
+  for (int i = threadIdx.x; i < ns; i += blockDim.x) {
+    if (sid[i] < 0) continue;
+    const unsigned long long k = rank_key(sdv[i], static_cast<unsigned>(sid[i]));
+    if (k < bound) pool[nk + atomicAdd(&ctrl[6], 1)] = k;
+  }
+  __syncthreads();
+  const int total = nk + ctrl[6];
+  int cnt         = min(total, KO);
+  int width       = P;  // keys handed to the sort
+  if (total <= 2 * P) {
+    while (width < total)
+      width <<= 1;
+    for (int i = threadIdx.x; i < width; i += blockDim.x)
+      sorted[i] = i < total ? pool[i] : kNoKey;
+  } else {
+    auto key_at         = [&](int i) { return pool[i]; };
     const radix_cut_t c = radix_cut(key_at, total, KO, hist, ctrl);
     if (threadIdx.x == 0) ctrl[0] = 0;
     __syncthreads();
     for (int i = threadIdx.x; i < total; i += blockDim.x) {
-      const unsigned long long k = key_at(i);
+      const unsigned long long k = pool[i];
       if ((k & c.mask) <= c.prefix) {
         const int s = atomicAdd(&ctrl[0], 1);
         if (s < P) sorted[s] = k;
       }
     }
-    cnt = KO;
-  } else {
-    for (int i = threadIdx.x; i < total; i += blockDim.x)
-      sorted[i] = key_at(i);
+    for (int i = KO + threadIdx.x; i < P; i += blockDim.x)
+      sorted[i] = kNoKey;
   }
-  for (int i = cnt + threadIdx.x; i < P; i += blockDim.x)
-    sorted[i] = kNoKey;
   __syncthreads();
-  bitonic_sort(sorted, P);
+  bitonic_sort(sorted, width);
   for (int i = threadIdx.x; i < KO; i += blockDim.x) {
     const unsigned long long k = i < cnt ? sorted[i] : kNoKey;
     pb[i] = k == kNoKey ? -1 : static_cast<long long>(static_cast<unsigned>(k & 0xffffffffULL));
@@ -369,8 +398,9 @@ __device__ __forceinline__ void merge_into_kept(unsigned long long* pool,
   }
 }
 
+
 template <bool kRows>
-__global__ void __launch_bounds__(kRoundThreads, 5) round_kernel(const round_args a)
+__global__ void __launch_bounds__(kRoundThreads, 4) round_kernel(const round_args a)
 {
   extern __shared__ __align__(16) int smem[];
   const round_layout lay(a);
@@ -503,8 +533,8 @@ __global__ void __launch_bounds__(kRoundThreads, 5) round_kernel(const round_arg
   // has four segments' loads in flight before it touches the set
   tick(0);
   const int HT = 1 << hash_log_of(total, a.log_cap);
-  for (int i = threadIdx.x; i < HT; i += blockDim.x)
-    table[i] = -1;
+  for (int i = threadIdx.x; i < HT / 4; i += blockDim.x)
+    reinterpret_cast<int4*>(table)[i] = make_int4(-1, -1, -1, -1);
   __syncthreads();
   {
     const int maxlen = kRows ? a.table_len : a.lr;
@@ -514,14 +544,16 @@ __global__ void __launch_bounds__(kRoundThreads, 5) round_kernel(const round_arg
     const int within0 = threadIdx.x & (lps - 1);
     const int spp     = kRoundThreads / lps;  // segments per pass
     const int seg0    = threadIdx.x / lps;
-    for (int w0 = within0; w0 < maxlen; w0 += lps) {
-      for (int sb = seg0; sb < nseg; sb += 4 * spp) {
+    // loop bounds are the same for every thread: the slot counter below is updated once per warp
+    for (int wb = 0; wb < maxlen; wb += lps) {
+      const int w0 = wb + within0;
+      for (int sb = 0; sb < nseg; sb += 4 * spp) {
         int v[4];
 #pragma unroll
         for (int u = 0; u < 4; u++) {
-          const int s = sb + u * spp;
+          const int s = sb + seg0 + u * spp;
           v[u]        = -1;
-          if (s < nseg) {
+          if (s < nseg && w0 < maxlen) {
             if constexpr (kRows) {
               v[u] = __ldg(a.table + static_cast<int64_t>(st[s]) * a.table_len + w0);
             } else {
@@ -529,24 +561,46 @@ __global__ void __launch_bounds__(kRoundThreads, 5) round_kernel(const round_arg
             }
           }
         }
+        int mine = 0;
 #pragma unroll
         for (int u = 0; u < 4; u++) {
           const int id = v[u];
-          if (id < 0) continue;  // nothing read, or the padding of a table row
-          unsigned s = (static_cast<unsigned>(id) * kIdHash) & (HT - 1);
-          for (int p = 0; p < HT; p++) {
-            const int prev = atomicCAS(&table[s], -1, id);
-            if (prev == -1) {
-              const int slot = atomicAdd(&ctrl[4], 1);
-              if (slot < a.nmax) cand[slot] = id;
-              // the sketch row of a new id will be wanted soon: start bringing it into L2
-              asm volatile("prefetch.global.L2 [%0];" ::"l"(a.sketch + static_cast<int64_t>(id) * S));
-              break;
+          bool is_new  = false;
+          if (id >= 0) {  // else nothing read, or the padding of a table row
+            unsigned s = (static_cast<unsigned>(id) * kIdHash) & (HT - 1);
+            for (int p = 0; p < HT; p++) {
+              const int prev = atomicCAS(&table[s], -1, id);
+              if (prev == -1) {
+                is_new = true;
+                // the sketch row of a new id will be wanted soon: start bringing it into L2
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(a.sketch + static_cast<int64_t>(id) * S));
+                break;
+              }
+              if (prev == id) break;
+              s = (s + 1) & (HT - 1);
             }
-            if (prev == id) break;
-            s = (s + 1) & (HT - 1);
           }
+          if (!is_new) v[u] = -1;
+          mine += is_new;
         }
+        // slots for the new ids of the whole warp with one update of the counter
+        __syncwarp();
+        int inc = mine;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int up = __shfl_up_sync(0xffffffffu, inc, o);
+          if (lane >= o) inc += up;
+        }
+        int base = 0;
+        if (lane == 31 && inc > 0) base = atomicAdd(&ctrl[4], inc);
+        base   = __shfl_sync(0xffffffffu, base, 31);
+        int at = base + inc - mine;
+#pragma unroll
+        for (int u = 0; u < 4; u++)
+          if (v[u] >= 0) {
+            if (at < a.nmax) cand[at] = v[u];
+            at++;
+          }
       }
     }
   }
@@ -554,31 +608,50 @@ __global__ void __launch_bounds__(kRoundThreads, 5) round_kernel(const round_arg
   const int n = min(ctrl[4], a.nmax);
   tick(1);
 
-  // int8 sketch distances (search_kernels.cuh:228-251): Lr lanes per row, one 16-byte chunk each,
-  // four rows per lane group in flight
+  // int8 sketch distances (search_kernels.cuh:228-251): one 8-code chunk per lane with its scale and
+  // query coordinates in registers, the chunks of a row summed by a butterfly over its lanes
+  // (strides 1, 2, 4, ...); four rows per lane group in flight. A sketch wider than 256 gives a
+  // lane a second chunk (c + 32), added last.
   {
-    int Lr = 1;
-    while (Lr < S / 16 && Lr < 32)
-      Lr <<= 1;
-    const int G = 32 / Lr, sub = lane % Lr;
+    const int chunks = S / 8;
+    int Lw           = 1;
+    while (Lw < chunks && Lw < 32)
+      Lw <<= 1;
+    const int G = 32 / Lw, sub = lane % Lw;
     const int rpp    = nw * G;  // rows per pass of the block
-    const bool live  = sub * 16 < S;
-    const float* scl = sc + (live ? sub * 16 : 0);
-    const float* qvl = qv + (live ? sub * 16 : 0);
+    const bool live  = sub < chunks;
+    const bool live2 = sub + 32 < chunks;
+    float cs[8], cq[8];
+#pragma unroll
+    for (int b = 0; b < 8; b++) {
+      cs[b] = live ? sc[sub * 8 + b] : 0.f;
+      cq[b] = live ? qv[sub * 8 + b] : 0.f;
+    }
     for (int jb = 0; jb < n; jb += 4 * rpp) {
-      int4 w[4];
+      uint2 w[4];
       int j[4];
 #pragma unroll
       for (int u = 0; u < 4; u++) {
-        j[u] = jb + u * rpp + warp * G + lane / Lr;
+        j[u] = jb + u * rpp + warp * G + lane / Lw;
         if (j[u] < n && live)
-          w[u] = __ldg(reinterpret_cast<const int4*>(a.sketch + static_cast<int64_t>(cand[j[u]]) * S + sub * 16));
+          w[u] = __ldg(reinterpret_cast<const uint2*>(a.sketch + static_cast<int64_t>(cand[j[u]]) * S + sub * 8));
       }
 #pragma unroll
       for (int u = 0; u < 4; u++) {
-        float d = (j[u] < n && live) ? sketch_chunk(w[u], scl, qvl) : 0.f;
-        for (int o = Lr >> 1; o; o >>= 1)
+        float d = (j[u] < n && live) ? sketch_chunk8(w[u], cs, cq) : 0.f;
+        for (int o = 1; o < Lw; o <<= 1)
           d = __fadd_rn(d, __shfl_xor_sync(0xffffffffu, d, o));
+        if (chunks > 32) {
+          float e = 0.f;
+          if (j[u] < n && live2) {
+            const uint2 w2 = __ldg(reinterpret_cast<const uint2*>(
+              a.sketch + static_cast<int64_t>(cand[j[u]]) * S + (sub + 32) * 8));
+            e = sketch_chunk8(w2, sc + (sub + 32) * 8, qv + (sub + 32) * 8);
+          }
+          for (int o = 1; o < 32; o <<= 1)
+            e = __fadd_rn(e, __shfl_xor_sync(0xffffffffu, e, o));
+          d = __fadd_rn(d, e);
+        }
         if (j[u] < n && sub == 0) dist[j[u]] = d;
       }
     }
@@ -710,7 +783,7 @@ __global__ void __launch_bounds__(kRoundThreads) final_rerank_kernel(const long 
   extern __shared__ __align__(16) int smem[];
   unsigned long long* pool   = reinterpret_cast<unsigned long long*>(smem);  // [k + R]
   unsigned long long* sorted = pool + ((k + R + 1) & ~1);                    // [P]
-  int* sid                   = reinterpret_cast<int*>(sorted + P);           // [R]
+  int* sid                   = reinterpret_cast<int*>(sorted + 2 * P);       // sorted [2 P]; sid [R]
   float* sdv                 = reinterpret_cast<float*>(sid + ((R + 3) & ~3));
   float* fq                  = sdv + ((R + 3) & ~3);                         // [D]
   unsigned* hist             = reinterpret_cast<unsigned*>(fq + ((D + 3) & ~3));
@@ -823,7 +896,7 @@ void final_rerank(const long long* si, int KO, int R, const __half* vectors, int
   int P = 2;
   while (P < k)
     P <<= 1;
-  const size_t words = 2 * static_cast<size_t>((k + R + 1) & ~1) + 2 * static_cast<size_t>(P) +
+  const size_t words = 2 * static_cast<size_t>((k + R + 1) & ~1) + 4 * static_cast<size_t>(P) +
                        2 * static_cast<size_t>((R + 3) & ~3) + ((D + 3) & ~3) + 256 + 16 + 8;
   final_rerank_kernel<<<m, kRoundThreads, sizeof(int) * words, s>>>(si, KO, R, vectors, D, Q, k, P, bi,
                                                                     bd, stats);

@@ -125,7 +125,7 @@ prepared prepare(const oracle_index& ix)
 
 // Squared distance of an fp16 row to an fp32 query (search_kernels.cuh:325-342). Summation
 // order shared with the CUDA path: element pair k feeds partial sum k mod 32 with two fused
-// multiply-adds, then a butterfly over the 32 partial sums (strides 16, 8, 4, 2, 1).
+// multiply-adds, then a butterfly over the 32 partial sums (strides 1, 2, 4, 8, 16).
 float exact_distance(const uint16_t* row, const float* q, int dim)
 {
   float part[32];
@@ -138,7 +138,7 @@ float exact_distance(const uint16_t* row, const float* q, int dim)
     float t = std::fma(a, a, part[k & 31]);
     part[k & 31] = std::fma(b, b, t);
   }
-  for (int o = 16; o; o >>= 1) {
+  for (int o = 1; o < 32; o <<= 1) {
     float nxt[32];
     for (int p = 0; p < 32; p++)
       nxt[p] = part[p] + part[p ^ o];
@@ -148,27 +148,27 @@ float exact_distance(const uint16_t* row, const float* q, int dim)
 }
 
 // int8 sketch distance sum_k (code_k * scale_k - qs_k)^2 (search_kernels.cuh:228-251):
-// chunk c of 16 codes feeds partial sum c sequentially; a butterfly over Lr partial sums,
-// Lr = the next power of two >= S / 16.
+// chunk c of 8 codes is partial sum c (two fused multiply-adds per code, in code order); a
+// butterfly over Lr partial sums (strides 1, 2, 4, ...), Lr = the next power of two >= S / 8.
 float sketch_distance(const int8_t* code, const float* scale, const float* qs, int S)
 {
   int Lr = 1;
-  while (Lr < S / 16 && Lr < 32)
-    Lr <<= 1;
-  float part[32];
+  while (Lr < S / 8)
+    Lr <<= 1;  // S <= 512: at most 64 partial sums
+  float part[64];
   for (int p = 0; p < Lr; p++)
     part[p] = 0.f;
-  for (int c = 0; c * 16 < S; c++) {
+  for (int c = 0; c * 8 < S; c++) {
     float d = 0.f;
-    for (int t = 0; t < 16; t++) {
-      int k   = c * 16 + t;
+    for (int t = 0; t < 8; t++) {
+      int k   = c * 8 + t;
       float u = std::fma(static_cast<float>(code[k]), scale[k], -qs[k]);
       d       = std::fma(u, u, d);
     }
-    part[c % Lr] += d;  // S <= 512 keeps c < Lr
+    part[c] = d;
   }
-  for (int o = Lr >> 1; o; o >>= 1) {
-    float nxt[32];
+  for (int o = 1; o < Lr; o <<= 1) {
+    float nxt[64];
     for (int p = 0; p < Lr; p++)
       nxt[p] = part[p] + part[p ^ o];
     std::memcpy(part, nxt, sizeof(float) * Lr);

@@ -197,8 +197,11 @@ __global__ void cell_codes_f32_kernel(const float* __restrict__ y, int64_t n, fl
 // ---- cell lookup -----------------------------------------------------------------------------
 
 // search_kernels.cuh:100-126: the finest level whose cell holds a list. One thread per
-// (query, copy); the codes of all levels are already there, so a level costs two dependent
-// reads (bucket bounds, then the short key scan) and no arithmetic.
+// (query, copy). The codes of all levels are already there, so the bucket bounds of every level
+// are fetched at once, then the first key of every non-empty bucket at once: two memory round
+// trips for the common case instead of two per level tried. The answer and the counters are those
+// of the level-by-level walk.
+constexpr int kProbeLevels = 8;  // levels handled in one sweep; more are walked in further sweeps
 __global__ void probe_kernel(const long long* __restrict__ codes,
                              int64_t pairs,
                              int C,
@@ -217,28 +220,52 @@ __global__ void probe_kernel(const long long* __restrict__ codes,
 {
   const int64_t t = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (t >= pairs) return;
-  const int c             = static_cast<int>(t % C);
-  const long long bmask   = (1LL << log_buckets) - 1;
-  int2 sg                 = make_int2(0, 0);
+  const int c           = static_cast<int>(t % C);
+  const long long bmask = (1LL << log_buckets) - 1;
+  int2 sg               = make_int2(0, 0);
   long long tried = 0, scanned = 0;
-  for (int j = 0; j < L; j++) {
-    if (level_on != nullptr && !level_on[c * L + j]) continue;
-    const long long h   = codes[t * L + j];
-    const int64_t cl    = static_cast<int64_t>(c) * L + j;
-    const int* o        = offsets + cl * T1 + static_cast<int>(h & bmask);
-    const int lo = o[0], hi = o[1];
-    const long long* kk = keys + cl * mmax;
-    tried++;
-    bool found = false;
-    for (int p = lo; p < hi; p++) {
-      scanned++;
-      if (kk[p] == h) {
-        sg    = make_int2((base[cl] + p) * list_len, lr);
-        found = true;
-        break;
+  bool found = false;
+  for (int j0 = 0; j0 < L && !found; j0 += kProbeLevels) {
+    long long h[kProbeLevels], k0[kProbeLevels];
+    int lo[kProbeLevels], hi[kProbeLevels];
+#pragma unroll
+    for (int u = 0; u < kProbeLevels; u++) {
+      const int j = j0 + u;
+      lo[u] = hi[u] = 0;
+      h[u]          = 0;
+      if (j < L && (level_on == nullptr || level_on[c * L + j])) {
+        h[u]         = codes[t * L + j];
+        const int* o = offsets + (static_cast<int64_t>(c) * L + j) * T1 + static_cast<int>(h[u] & bmask);
+        lo[u]        = __ldg(o);
+        hi[u]        = __ldg(o + 1);
+        if (hi[u] <= lo[u]) hi[u] = lo[u] - 1;  // mark "tried, empty bucket"
+      } else {
+        hi[u] = lo[u] - 2;  // not a level to try
       }
     }
-    if (found) break;
+#pragma unroll
+    for (int u = 0; u < kProbeLevels; u++) {
+      k0[u] = 0;
+      if (hi[u] > lo[u])
+        k0[u] = __ldg(keys + (static_cast<int64_t>(c) * L + j0 + u) * mmax + lo[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < kProbeLevels; u++) {
+      if (found || hi[u] == lo[u] - 2) continue;
+      tried++;
+      if (hi[u] < lo[u]) continue;  // empty bucket
+      const int64_t cl    = static_cast<int64_t>(c) * L + j0 + u;
+      const long long* kk = keys + cl * mmax;
+      for (int p = lo[u]; p < hi[u]; p++) {
+        scanned++;
+        const long long key = p == lo[u] ? k0[u] : __ldg(kk + p);
+        if (key == h[u]) {
+          sg    = make_int2((base[cl] + p) * list_len, lr);
+          found = true;
+          break;
+        }
+      }
+    }
   }
   seg[t] = sg;
   if (stats != nullptr) {

@@ -208,12 +208,10 @@ __device__ __forceinline__ float sketch_chunk8(uint2 w, const float* s, const fl
   return d;
 }
 
-/// Rows j and j + stride of a lane group: squared distances of two fp16 rows to the query.
-/// kRegs: the row has at most two 16-byte steps per lane (D <= 128) and the lane's query
-/// coordinates qr[16] live in registers; otherwise they are read from shared memory (fq).
-template <bool kRegs>
+/// Rows j and j + stride of a lane group: squared distances of two fp16 rows to the query fq
+/// (shared memory, read 16 bytes at a time).
 __device__ __forceinline__ void exact_pair(const uint4* const (&row)[2], int D, int sub, const float* fq,
-                                           const float (&qr)[16], float (&out)[2])
+                                           float (&out)[2])
 {
   float acc[2][4];
 #pragma unroll
@@ -232,23 +230,24 @@ __device__ __forceinline__ void exact_pair(const uint4* const (&row)[2], int D, 
 #pragma unroll
     for (int s = 0; s < 2; s++) {
       const int hs = h0 + 64 * s;
-      if (hs >= D) break;
+      if (hs < D) {
+        const float4 q0 = *reinterpret_cast<const float4*>(fq + hs);
+        const float4 q1 = *reinterpret_cast<const float4*>(fq + hs + 4);
+        const float qq[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
 #pragma unroll
-      for (int u = 0; u < 2; u++) {
-        if (row[u] == nullptr) continue;
-        const __half2* h2 = reinterpret_cast<const __half2*>(&v[s][u]);
+        for (int u = 0; u < 2; u++) {
+          if (row[u] == nullptr) continue;
+          const __half2* h2 = reinterpret_cast<const __half2*>(&v[s][u]);
 #pragma unroll
-        for (int t = 0; t < 4; t++) {
-          const float2 x = __half22float2(h2[t]);
-          const float qa = kRegs ? qr[8 * s + 2 * t] : fq[hs + 2 * t];
-          const float qb = kRegs ? qr[8 * s + 2 * t + 1] : fq[hs + 2 * t + 1];
-          const float a  = __fsub_rn(x.x, qa);
-          const float b  = __fsub_rn(x.y, qb);
-          acc[u][t]      = __fmaf_rn(b, b, __fmaf_rn(a, a, acc[u][t]));
+          for (int t = 0; t < 4; t++) {
+            const float2 x = __half22float2(h2[t]);
+            const float a  = __fsub_rn(x.x, qq[2 * t]);
+            const float b  = __fsub_rn(x.y, qq[2 * t + 1]);
+            acc[u][t]      = __fmaf_rn(b, b, __fmaf_rn(a, a, acc[u][t]));
+          }
         }
       }
     }
-    if (kRegs) break;
   }
   // butterfly over the 32 partial sums, strides 1, 2 (inside the lane), then 4, 8, 16 (lanes)
 #pragma unroll
@@ -273,13 +272,6 @@ __device__ __forceinline__ void exact_distances(
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   if ((D & 7) == 0) {
     const int sub = lane & 7, grp = lane >> 3;
-    const bool regs = D <= 128;
-    float qr[16];
-#pragma unroll
-    for (int i = 0; i < 16; i++) {
-      const int h = 8 * sub + 64 * (i >> 3) + (i & 7);
-      qr[i]       = (regs && h < D) ? fq[h] : 0.f;
-    }
     for (int jb = 0; jb < ns; jb += nw * 8) {
       int j[2];
       const uint4* row[2];
@@ -290,10 +282,7 @@ __device__ __forceinline__ void exact_distances(
         row[u] = id >= 0 ? reinterpret_cast<const uint4*>(vectors + static_cast<int64_t>(id) * D) : nullptr;
       }
       float out[2];
-      if (regs)
-        exact_pair<true>(row, D, sub, fq, qr, out);
-      else
-        exact_pair<false>(row, D, sub, fq, qr, out);
+      exact_pair(row, D, sub, fq, out);
 #pragma unroll
       for (int u = 0; u < 2; u++)
         if (row[u] != nullptr && sub == 0) sdv[j[u]] = out[u];

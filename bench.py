@@ -46,6 +46,7 @@ WORKLOADS = {
                    sketch_width=64, table_len=32)),
 }
 LADDER = [
+    dict(read=8, starts=24, waves=2, rerank=128, wave_rerank=256),
     dict(read=8, starts=32, waves=2, rerank=256, wave_rerank=256),
     dict(read=32, starts=32, waves=2, rerank=256, wave_rerank=256),
     dict(read=32, starts=32, waves=3, rerank=256, wave_rerank=256),

@@ -14,7 +14,7 @@ constexpr int kMaxRerank   = 512;    // exact rerank depth per round
 constexpr int kMaxKeepSort = 1024;   // kept + reranked keys sorted together (exact ranking)
 constexpr int kMaxSketchKO = 1024;   // kept entries when ranking by sketch
 constexpr int kMaxExpanded = 6144;   // start points expanded by earlier waves
-constexpr int kRoundThreads = 256;
+constexpr int kRoundThreads = 128;
 
 /// Rows [from, m) of q become copies of row 0 (padding of a partial batch).
 void pad_rows(float* q, int from, int m, int D, cudaStream_t s);

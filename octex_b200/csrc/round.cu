@@ -389,7 +389,7 @@ __device__ __forceinline__ void merge_into_kept(unsigned long long* pool,
 
 
 template <bool kRows>
-__global__ void __launch_bounds__(kRoundThreads, 4) round_kernel(const round_args a)
+__global__ void __launch_bounds__(kRoundThreads, 8) round_kernel(const round_args a)
 {
   extern __shared__ __align__(16) int smem[];
   const round_layout lay(a);
@@ -830,7 +830,7 @@ __global__ void merge_kept_kernel(const long long* __restrict__ src_i,
   bitonic_sort(mk, P);  // by (id, distance): the first key of an id run is its nearest copy
   const int per = (P + kRoundThreads - 1) / kRoundThreads;
   const int i0  = threadIdx.x * per;
-  unsigned long long mine[16];
+  unsigned long long mine[4096 / kRoundThreads];
   int cnt = 0;
   for (int i = i0; i < min(P, i0 + per); i++) {
     const unsigned long long k = mk[i];

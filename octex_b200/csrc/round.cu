@@ -37,11 +37,16 @@ struct round_layout {
       at += (n + 3) & ~3;  // keep every region 16-byte aligned
       return o;
     };
-    table  = take(a.ht_slots);
-    cand   = take(in_smem);
-    dist   = take(in_smem);
-    pool   = take(2 * (a.KO + rm));
-    sorted = take(4 * a.P);
+    // Two regions are used twice. The sketch distances are written where the hash set of the gather
+    // was (the set is dead once the ids are collected; the filter of kept ids, which builds a small
+    // set there again, starts after the selection has copied out the distances it needs). The keys of
+    // the merge are written where the candidates were (dead after the selection).
+    const int pool_words = 2 * (a.KO + rm);
+    table  = take(a.ht_slots > in_smem ? a.ht_slots : in_smem);
+    dist   = table;
+    cand   = take(in_smem > pool_words + 4 * a.P ? in_smem : pool_words + 4 * a.P);
+    pool   = cand;
+    sorted = cand + pool_words;
     sid    = take(rm);
     sdv    = take(rm);
     qv     = take(a.sw);
@@ -60,8 +65,9 @@ struct round_layout {
 
 __device__ __forceinline__ int hash_log_of(int total, int log_cap)
 {
-  // smallest e in [kMinLogHash, log_cap] with 2^e >= 1.5 * total (search_kernels.cuh:33-38)
-  const int need = (3 * total + 1) / 2;
+  // smallest e in [kMinLogHash, log_cap] with 2^e >= 4/3 * total: the set is at most three quarters
+  // full (search_kernels.cuh:33-38 sizes it for two thirds; only the memory it takes differs)
+  const int need = (4 * total + 2) / 3;
   int e          = kMinLogHash;
   while (e < log_cap && (1 << e) < need)
     e++;

@@ -41,7 +41,7 @@ constexpr size_t kSmemHardLimit = size_t{227} << 10;  // shared memory a block c
 /// Fill the size fields of a round and decide where its candidate arrays live.
 void size_round(plan& pl, kernels::round_args& r, int entries_max, int pick_entries, int device)
 {
-  r.log_cap = std::clamp(log2_ceil((3 * int64_t{entries_max} + 1) / 2), kernels::kMinLogHash,
+  r.log_cap = std::clamp(log2_ceil((4 * int64_t{entries_max} + 2) / 3), kernels::kMinLogHash,
                          log2_ceil(kernels::kMaxHash));
   r.pick_slots = 0;
   if (pick_entries > 0) {
@@ -49,7 +49,10 @@ void size_round(plan& pl, kernels::round_args& r, int entries_max, int pick_entr
     while (r.pick_slots * 3 < pick_entries * 4)  // at most 75 % full
       r.pick_slots <<= 1;
   }
-  r.ht_slots = std::max(1 << r.log_cap, r.pick_slots);
+  int kept_slots = 64;  // the set of kept ids a round filters its selection with
+  while (kept_slots < 2 * r.KO)
+    kept_slots <<= 1;
+  r.ht_slots = std::max({1 << r.log_cap, r.pick_slots, kept_slots});
   r.nmax     = std::max(entries_max, 1);
   r.P = 2;
   while (r.P < r.KO)

@@ -47,9 +47,10 @@ bool project_tc_supported(int blocks, int ldu);
 void project_tc_setup(project_tc_plan& p, const __half* qh, int m, const __half* ut, int copies, int ldu);
 /// codes [m, copies, L] (and Yout [m, copies * 32] fp16 when not null) from the operands of the
 /// plan. *error (device-visible int) becomes non-zero when a wait inside the kernel ran out.
+/// finest = the smallest spacing (host copy): coordinates small against it take the short decode.
 void project_decode_tc(const project_tc_plan& p, int L, const __half* shift, const float* inv_f,
-                       const unsigned char* level_on, long long* codes, __half* Yout, int* error,
-                       cudaStream_t s);
+                       float finest, const unsigned char* level_on, long long* codes, __half* Yout,
+                       int* error, cudaStream_t s);
 
 /// codes [n] = cell code of each row of y [n, 8*blocks] float32 scaled by inv_f.
 void cell_codes_f32(const float* y, int64_t n, int blocks, float inv_f, long long* codes,

@@ -188,10 +188,15 @@ __global__ void cell_codes_f32_kernel(const float* __restrict__ y, int64_t n, fl
   const int64_t t = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (t >= n) return;
   float v[8 * B];
+  // rows small against the spacing take the short decode, as in the projection's epilogue
+  const float tame_y = inv_f > 0.f ? 0.99f * kTameLimit / inv_f : 0.f;
+  bool wild          = false;
 #pragma unroll
-  for (int i = 0; i < 8 * B; i++)
+  for (int i = 0; i < 8 * B; i++) {
     v[i] = y[t * 8 * B + i];
-  codes[t] = cell_code<B>(v, inv_f);
+    wild = wild || !(fabsf(v[i]) < tame_y);
+  }
+  codes[t] = wild ? cell_code<B>(v, inv_f) : cell_code_tame<B>(v, inv_f);
 }
 
 // ---- cell lookup -----------------------------------------------------------------------------

@@ -136,6 +136,7 @@ __global__ void __launch_bounds__(kThreads, 3) project_decode_tc_kernel(
   int nkb,
   const __half* __restrict__ shift,
   const float* __restrict__ inv_f,
+  float tame_y,
   const unsigned char* __restrict__ level_on,
   long long* __restrict__ codes,
   __half* __restrict__ Yout,
@@ -241,10 +242,12 @@ __global__ void __launch_bounds__(kThreads, 3) project_decode_tc_kernel(
     if (!ready || row >= m || c >= Cg) continue;
     float y[32];
     __align__(16) __half yh[32];
+    bool wild = false;  // a coordinate too large for the short decode (or not a number)
 #pragma unroll
     for (int i = 0; i < 32; i++) {
       yh[i] = __float2half_rn(__fadd_rn(__uint_as_float(r[i]), sm.shift[cc * 32 + i]));
       y[i]  = __half2float(yh[i]);
+      wild  = wild || !(fabsf(y[i]) < tame_y);
     }
     if (Yout != nullptr) {
       uint4* dst = reinterpret_cast<uint4*>(Yout + static_cast<int64_t>(row) * N + c * 32);
@@ -255,7 +258,8 @@ __global__ void __launch_bounds__(kThreads, 3) project_decode_tc_kernel(
     long long* out = codes + (static_cast<int64_t>(row) * Cg + c) * L;
     for (int j = 0; j < L; j++) {
       long long h = 0;
-      if (level_on == nullptr || level_on[c * L + j]) h = cell_code<4>(y, sm.inv_f[j]);
+      if (level_on == nullptr || level_on[c * L + j])
+        h = wild ? cell_code<4>(y, sm.inv_f[j]) : cell_code_tame<4>(y, sm.inv_f[j]);
       out[j] = h;
     }
   }
@@ -321,16 +325,18 @@ void project_tc_setup(project_tc_plan& p, const __half* qh, int m, const __half*
 }
 
 void project_decode_tc(const project_tc_plan& p, int L, const __half* shift, const float* inv_f,
-                       const unsigned char* level_on, long long* codes, __half* Yout, int* error,
-                       cudaStream_t s)
+                       float finest, const unsigned char* level_on, long long* codes, __half* Yout,
+                       int* error, cudaStream_t s)
 {
+  // |y| below this keeps |y / spacing| under the bound of the short decode at every level
+  const float tame_y = finest > 0.f ? kTameLimit * finest * 0.99f : 0.f;
   if (p.m <= 0 || p.copies <= 0) return;
   CUtensorMap a, b;
   std::memcpy(&a, p.map_a, sizeof(a));
   std::memcpy(&b, p.map_b, sizeof(b));
   dim3 grid((p.copies * 32 + kTileN - 1) / kTileN, (p.m + kTileM - 1) / kTileM);
   project_decode_tc_kernel<<<grid, kThreads, sizeof(tc_smem) + 1024, s>>>(
-    a, b, p.m, p.copies, L, p.ldu / kTileK, shift, inv_f, level_on, codes, Yout, error);
+    a, b, p.m, p.copies, L, p.ldu / kTileK, shift, inv_f, tame_y, level_on, codes, Yout, error);
 }
 
 }  // namespace octex_b200::kernels

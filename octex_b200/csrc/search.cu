@@ -123,7 +123,10 @@ void run_batch(index_impl const& ix, plan& pl, cudaStream_t s, std::vector<cudaE
   const unsigned char* levels = pl.dbg.taps ? nullptr : p.level_on.as<unsigned char>();
   if (pl.use_tc) {
     // tensor cores; the projected coordinates stay in TMEM unless they are asked for
-    kernels::project_decode_tc(pl.tc, L, p.shift.as<__half>(), p.inv_f.as<float>(), levels,
+    float finest = ix.spacings[0];
+    for (float f : ix.spacings)
+      finest = std::min(finest, f);
+    kernels::project_decode_tc(pl.tc, L, p.shift.as<__half>(), p.inv_f.as<float>(), finest, levels,
                                pl.codes.as<long long>(), pl.dbg.taps ? pl.Y.as<__half>() : nullptr,
                                pl.tc_error_dev, s);
     mark();

@@ -63,6 +63,24 @@ def test_cell_codes_bit_exact(oracle, golden):
         assert len(bad) <= 4 and (bad < 32).all(), (name, bad)
 
 
+def test_cell_codes_large_coordinates(oracle):
+    """Rows small against the spacing take a shorter decode on the GPU (|y / spacing| < 2^20); rows
+    beyond it, and rows that mix both, take the general one. Both must give the checker's codes."""
+    rng = np.random.default_rng(17)
+    n = 40000
+    for inv in (1.0, 0.4, 16.0):
+        edge = 2.0 ** 20 / inv
+        x = rng.uniform(-6, 6, size=(n, 32)).astype(np.float32)
+        x[: n // 4] *= np.float32(edge / 6 * 0.98)                  # just inside the bound
+        x[n // 4: n // 2] *= np.float32(edge / 6 * 1.5)             # outside
+        x[n // 2: 3 * n // 4, ::5] = np.float32(edge * 1.01)        # one large coordinate in five
+        x[3 * n // 4:, 3] = np.float32(65504.0)                     # the largest fp16 value
+        x = np.concatenate([x, np.round(x[:2000] * 2) * np.float32(0.5)])  # exact half-integers
+        got = octex_b200.cell_codes(x, 4, inv)
+        want = oracle.cell_code(x, 4, float(np.float32(inv)))
+        assert np.array_equal(got, want), (inv, int((got != want).sum()))
+
+
 def test_cell_codes_against_reference_device_code(oracle):
     """The reference's e8b_hash64 compiled as device code, run on this GPU, on the same points."""
     if oracle.ref_e8_cuda() is None:

@@ -46,6 +46,7 @@ WORKLOADS = {
                    sketch_width=64, table_len=32)),
 }
 LADDER = [
+    dict(read=16, starts=32, waves=1, rerank=128, wave_rerank=384),
     dict(read=8, starts=24, waves=2, rerank=128, wave_rerank=256),
     dict(read=8, starts=32, waves=2, rerank=256, wave_rerank=256),
     dict(read=32, starts=32, waves=2, rerank=256, wave_rerank=256),
@@ -282,6 +283,7 @@ def main():
     prof = {}
     for _ in range(args.steps):
         flush.fill_(1)
+        torch.cuda.synchronize()  # the fill runs on torch's stream, the batch on the library's
         for name, ms in idx.profile_batch(nq, K, **sp):
             key = name.split("[")[0]
             prof.setdefault(key, []).append(ms)

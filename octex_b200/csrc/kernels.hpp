@@ -8,13 +8,23 @@
 
 namespace octex_b200::kernels {
 
-constexpr int kMinLogHash  = 11;     // smallest per-query hash set: 2^11 slots
+constexpr int kMinHash     = 256;    // smallest per-query hash set (slots)
 constexpr int kMaxHash     = 32768;  // largest per-query hash set
 constexpr int kMaxRerank   = 512;    // exact rerank depth per round
 constexpr int kMaxKeepSort = 1024;   // kept + reranked keys sorted together (exact ranking)
 constexpr int kMaxSketchKO = 1024;   // kept entries when ranking by sketch
 constexpr int kMaxExpanded = 6144;   // start points expanded by earlier waves
 constexpr int kRoundThreads = 128;
+
+/// Slots of the hash set that collects `total` entries: at most three quarters full, a multiple of
+/// four, between kMinHash and cap. (The reference, search_kernels.cuh:33-38, takes a power of two at
+/// most two thirds full; only the memory taken differs.)
+__host__ __device__ inline int hash_slots_of(int total, int cap)
+{
+  int need = ((4 * total + 2) / 3 + 3) & ~3;
+  if (need < kMinHash) need = kMinHash;
+  return need < cap ? need : cap;
+}
 
 /// Rows [from, m) of q become copies of row 0 (padding of a partial batch).
 void pad_rows(float* q, int from, int m, int D, cudaStream_t s);
@@ -96,7 +106,7 @@ struct round_args {
   float* sd = nullptr;      // kept distances [m, KO]
   // sizes of the shared-memory carve-up (host decides)
   int ht_slots = 0;   // ints of the hash set region (>= largest set used, >= pick_slots)
-  int log_cap = 0;    // log2 of the largest gather hash set
+  int cap_slots = 0;  // largest gather hash set (slots)
   int nmax = 0;       // capacity of the candidate / distance arrays
   int P = 0;          // keys sorted by the merge (power of two >= KO)
   int* cand_global = nullptr;    // [m, nmax] when the candidates do not fit shared memory

@@ -36,9 +36,9 @@ __global__ void pad_rows_kernel(float* __restrict__ q, int from, int m, int D)
 
 // Centre (search_kernels.cuh:57-69) fused with the sketch-space projection of the query
 // (search.cu:321-341): a block takes kCenterRows queries, their centred copies sit in shared
-// memory, thread s owns sketch coordinate s of all of them, so every element of the basis is read
-// once per block; each (query, coordinate) sum runs over the dimensions in order.
-constexpr int kCenterRows = 8;
+// memory, a thread owns one sketch coordinate of eight of them, so an element of the basis is read
+// once per eight queries; each (query, coordinate) sum runs over the dimensions in order.
+constexpr int kCenterRows = 16;
 __global__ void __launch_bounds__(128) center_sketch_kernel(const float* __restrict__ q,
                                                             const float* __restrict__ mean,
                                                             const float* __restrict__ basis,
@@ -49,34 +49,60 @@ __global__ void __launch_bounds__(128) center_sketch_kernel(const float* __restr
                                                             int ldq,
                                                             float* __restrict__ qs)
 {
-  extern __shared__ float qc[];  // [kCenterRows][D]
+  extern __shared__ __align__(16) float qc[];  // [D][kCenterRows]: the rows of a dimension side by side
   const int row0 = blockIdx.x * kCenterRows;
   const int rows = min(kCenterRows, m - row0);
+  // fp16 copies, consecutive threads on consecutive dimensions
   for (int i = threadIdx.x; i < rows * ldq; i += blockDim.x) {
     const int r = i / ldq, d = i - r * ldq;
-    float v = 0.f;
-    if (d < D) {
-      v             = __fsub_rn(q[static_cast<int64_t>(row0 + r) * D + d], mean[d]);
-      qc[r * D + d] = v;
-    }
+    const float v = d < D ? __fsub_rn(q[static_cast<int64_t>(row0 + r) * D + d], mean[d]) : 0.f;
     qh[static_cast<int64_t>(row0 + r) * ldq + d] = __float2half_rn(v);
   }
-  for (int i = rows * D + threadIdx.x; i < kCenterRows * D; i += blockDim.x)
-    qc[i] = 0.f;
+  // fp32 copies for the sketch, stored in the order the threads run (row fastest)
+  for (int i = threadIdx.x; i < kCenterRows * D; i += blockDim.x) {
+    const int r = i % kCenterRows, d = i / kCenterRows;
+    qc[d * kCenterRows + r] = r < rows ? __fsub_rn(q[static_cast<int64_t>(row0 + r) * D + d], mean[d]) : 0.f;
+  }
   __syncthreads();
-  for (int s = threadIdx.x; s < S; s += blockDim.x) {
-    float acc[kCenterRows];
+  // an item = (group of 8 rows, sketch coordinate): 8 sums, each over the dimensions in order
+  constexpr int kGroups = kCenterRows / 8;
+  for (int item = threadIdx.x; item < kGroups * S; item += blockDim.x) {
+    const int g = item / S, s = item - g * S;
+    float acc[8];
 #pragma unroll
-    for (int r = 0; r < kCenterRows; r++)
+    for (int r = 0; r < 8; r++)
       acc[r] = 0.f;
-    for (int d = 0; d < D; d++) {
-      const float b = basis[static_cast<int64_t>(d) * S + s];
+    const float* col = basis + s;
+    const float* own = qc + 8 * g;
+    int d = 0;
+    for (; d + 8 <= D; d += 8) {
+      float b[8];
 #pragma unroll
-      for (int r = 0; r < kCenterRows; r++)
-        acc[r] = __fmaf_rn(qc[r * D + d], b, acc[r]);
+      for (int u = 0; u < 8; u++)
+        b[u] = __ldg(col + static_cast<int64_t>(d + u) * S);
+#pragma unroll
+      for (int u = 0; u < 8; u++) {
+        const float4 x0 = *reinterpret_cast<const float4*>(own + (d + u) * kCenterRows);
+        const float4 x1 = *reinterpret_cast<const float4*>(own + (d + u) * kCenterRows + 4);
+        acc[0] = __fmaf_rn(x0.x, b[u], acc[0]);
+        acc[1] = __fmaf_rn(x0.y, b[u], acc[1]);
+        acc[2] = __fmaf_rn(x0.z, b[u], acc[2]);
+        acc[3] = __fmaf_rn(x0.w, b[u], acc[3]);
+        acc[4] = __fmaf_rn(x1.x, b[u], acc[4]);
+        acc[5] = __fmaf_rn(x1.y, b[u], acc[5]);
+        acc[6] = __fmaf_rn(x1.z, b[u], acc[6]);
+        acc[7] = __fmaf_rn(x1.w, b[u], acc[7]);
+      }
     }
-    for (int r = 0; r < rows; r++)
-      qs[static_cast<int64_t>(row0 + r) * S + s] = acc[r];
+    for (; d < D; d++) {
+      const float b = __ldg(col + static_cast<int64_t>(d) * S);
+#pragma unroll
+      for (int r = 0; r < 8; r++)
+        acc[r] = __fmaf_rn(own[d * kCenterRows + r], b, acc[r]);
+    }
+#pragma unroll
+    for (int r = 0; r < 8; r++)
+      if (8 * g + r < rows) qs[static_cast<int64_t>(row0 + 8 * g + r) * S + s] = acc[r];
   }
 }
 

@@ -63,15 +63,10 @@ struct round_layout {
   }
 };
 
-__device__ __forceinline__ int hash_log_of(int total, int log_cap)
+/// Home slot of an id in a set of `slots` (any size): the high word of hash * slots.
+__device__ __forceinline__ unsigned home_slot(int id, int slots)
 {
-  // smallest e in [kMinLogHash, log_cap] with 2^e >= 4/3 * total: the set is at most three quarters
-  // full (search_kernels.cuh:33-38 sizes it for two thirds; only the memory it takes differs)
-  const int need = (4 * total + 2) / 3;
-  int e          = kMinLogHash;
-  while (e < log_cap && (1 << e) < need)
-    e++;
-  return e;
+  return __umulhi(static_cast<unsigned>(id) * kIdHash, static_cast<unsigned>(slots));
 }
 
 /// Exclusive prefix of v over the block (kRoundThreads threads); total = the sum.
@@ -527,7 +522,7 @@ __global__ void __launch_bounds__(kRoundThreads, 8) round_kernel(const round_arg
   // threads walks one segment, so consecutive threads read consecutive entries, and every thread
   // has four segments' loads in flight before it touches the set
   tick(0);
-  const int HT = 1 << hash_log_of(total, a.log_cap);
+  const int HT = hash_slots_of(total, a.cap_slots);
   for (int i = threadIdx.x; i < HT / 4; i += blockDim.x)
     reinterpret_cast<int4*>(table)[i] = make_int4(-1, -1, -1, -1);
   __syncthreads();
@@ -562,7 +557,7 @@ __global__ void __launch_bounds__(kRoundThreads, 8) round_kernel(const round_arg
           const int id = v[u];
           bool is_new  = false;
           if (id >= 0) {  // else nothing read, or the padding of a table row
-            unsigned s = (static_cast<unsigned>(id) * kIdHash) & (HT - 1);
+            unsigned s = home_slot(id, HT);
             for (int p = 0; p < HT; p++) {
               const int prev = atomicCAS(&table[s], -1, id);
               if (prev == -1) {
@@ -572,7 +567,7 @@ __global__ void __launch_bounds__(kRoundThreads, 8) round_kernel(const round_arg
                 break;
               }
               if (prev == id) break;
-              s = (s + 1) & (HT - 1);
+              s = s + 1 == static_cast<unsigned>(HT) ? 0u : s + 1;
             }
           }
           if (!is_new) v[u] = -1;

@@ -18,14 +18,6 @@ namespace detail {
 
 namespace {
 
-auto log2_ceil(int64_t v) -> int
-{
-  int e = 0;
-  while ((int64_t{1} << e) < v)
-    e++;
-  return e;
-}
-
 template <typename T>
 auto alloc(plan& pl, int device, int64_t count, int fill = -2) -> dbuf
 {
@@ -41,8 +33,7 @@ constexpr size_t kSmemHardLimit = size_t{227} << 10;  // shared memory a block c
 /// Fill the size fields of a round and decide where its candidate arrays live.
 void size_round(plan& pl, kernels::round_args& r, int entries_max, int pick_entries, int device)
 {
-  r.log_cap = std::clamp(log2_ceil((4 * int64_t{entries_max} + 2) / 3), kernels::kMinLogHash,
-                         log2_ceil(kernels::kMaxHash));
+  r.cap_slots  = kernels::hash_slots_of(std::min(entries_max, kernels::kMaxHash), kernels::kMaxHash);
   r.pick_slots = 0;
   if (pick_entries > 0) {
     r.pick_slots = 64;
@@ -52,7 +43,7 @@ void size_round(plan& pl, kernels::round_args& r, int entries_max, int pick_entr
   int kept_slots = 64;  // the set of kept ids a round filters its selection with
   while (kept_slots < 2 * r.KO)
     kept_slots <<= 1;
-  r.ht_slots = std::max({1 << r.log_cap, r.pick_slots, kept_slots});
+  r.ht_slots = std::max({r.cap_slots, r.pick_slots, kept_slots});
   r.nmax     = std::max(entries_max, 1);
   r.P = 2;
   while (r.P < r.KO)

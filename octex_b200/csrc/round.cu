@@ -209,8 +209,54 @@ __device__ __forceinline__ float sketch_chunk8(uint2 w, const float* s, const fl
   return d;
 }
 
+/// Sketch distances of the candidates cand[0, n) into dist[0, n) for a sketch of at most 32 chunks
+/// of eight codes: kLw (a power of two >= chunks) lanes own a row, one chunk each with its scale
+/// and query coordinates in registers; the chunk sums of a row are added by a butterfly over its
+/// lanes (strides 1, 2, 4, ...); a lane group has four rows in flight. Straight-line code: a lane
+/// past the last row or past the last chunk works on a valid stand-in and its result is dropped
+/// (a chunk past the end has scale and query 0, so it adds exactly 0).
+template <int kLw>
+__device__ __forceinline__ void sketch_rows(const int* cand, int n, const signed char* __restrict__ sketch,
+                                            int S, const float* sc, const float* qv, float* dist)
+{
+  constexpr int kG = 32 / kLw;  // rows per warp and step
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int sub = lane % kLw, grp = lane / kLw;
+  const int chunks = S / 8;
+  const bool live  = sub < chunks;
+  const int subc   = live ? sub : 0;
+  float cs[8], cq[8];
+#pragma unroll
+  for (int b = 0; b < 8; b++) {
+    cs[b] = live ? sc[sub * 8 + b] : 0.f;
+    cq[b] = live ? qv[sub * 8 + b] : 0.f;
+  }
+  const int rpp = nw * kG;  // rows per step of the block
+  for (int jb = 0; jb < n; jb += 4 * rpp) {
+    uint2 w[4];
+    int j[4];
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+      j[u]         = jb + u * rpp + warp * kG + grp;
+      const int id = cand[min(j[u], n - 1)];
+      w[u] = __ldg(reinterpret_cast<const uint2*>(sketch + static_cast<int64_t>(id) * S) + subc);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+      float d = sketch_chunk8(w[u], cs, cq);
+#pragma unroll
+      for (int o = 1; o < kLw; o <<= 1)
+        d = __fadd_rn(d, __shfl_xor_sync(0xffffffffu, d, o));
+      if (j[u] < n && sub == 0) dist[j[u]] = d;
+    }
+  }
+}
+
 /// Rows j and j + stride of a lane group: squared distances of two fp16 rows to the query fq
 /// (shared memory, read 16 bytes at a time).
+/// Both row pointers are valid (a row that is not wanted is replaced by any row by the caller, who
+/// drops the result). kWhole: D is a multiple of 128, so no step needs a bounds check.
+template <bool kWhole>
 __device__ __forceinline__ void exact_pair(const uint4* const (&row)[2], int D, int sub, const float* fq,
                                            float (&out)[2])
 {
@@ -227,17 +273,16 @@ __device__ __forceinline__ void exact_pair(const uint4* const (&row)[2], int D, 
     for (int s = 0; s < 2; s++)
 #pragma unroll
       for (int u = 0; u < 2; u++)
-        if (row[u] != nullptr && h0 + 64 * s < D) v[s][u] = __ldg(row[u] + ((h0 + 64 * s) >> 3));
+        if (kWhole || h0 + 64 * s < D) v[s][u] = __ldg(row[u] + ((h0 + 64 * s) >> 3));
 #pragma unroll
     for (int s = 0; s < 2; s++) {
       const int hs = h0 + 64 * s;
-      if (hs < D) {
+      if (kWhole || hs < D) {
         const float4 q0 = *reinterpret_cast<const float4*>(fq + hs);
         const float4 q1 = *reinterpret_cast<const float4*>(fq + hs + 4);
         const float qq[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
 #pragma unroll
         for (int u = 0; u < 2; u++) {
-          if (row[u] == nullptr) continue;
           const __half2* h2 = reinterpret_cast<const __half2*>(&v[s][u]);
 #pragma unroll
           for (int t = 0; t < 4; t++) {
@@ -275,18 +320,24 @@ __device__ __forceinline__ void exact_distances(
     const int sub = lane & 7, grp = lane >> 3;
     for (int jb = 0; jb < ns; jb += nw * 8) {
       int j[2];
+      bool wanted[2];
       const uint4* row[2];
 #pragma unroll
       for (int u = 0; u < 2; u++) {
         j[u]         = jb + u * nw * 4 + warp * 4 + grp;
         const int id = j[u] < ns ? sid[j[u]] : -1;
-        row[u] = id >= 0 ? reinterpret_cast<const uint4*>(vectors + static_cast<int64_t>(id) * D) : nullptr;
+        wanted[u]    = id >= 0;
+        // a slot without a row works on row 0 (cached after its first use) and drops the result
+        row[u] = reinterpret_cast<const uint4*>(vectors + static_cast<int64_t>(wanted[u] ? id : 0) * D);
       }
       float out[2];
-      exact_pair(row, D, sub, fq, out);
+      if ((D & 127) == 0)
+        exact_pair<true>(row, D, sub, fq, out);
+      else
+        exact_pair<false>(row, D, sub, fq, out);
 #pragma unroll
       for (int u = 0; u < 2; u++)
-        if (row[u] != nullptr && sub == 0) sdv[j[u]] = out[u];
+        if (wanted[u] && sub == 0) sdv[j[u]] = out[u];
     }
   } else {
     for (int j = warp; j < ns; j += nw) {
@@ -602,7 +653,20 @@ __global__ void __launch_bounds__(kRoundThreads, 8) round_kernel(const round_arg
   // query coordinates in registers, the chunks of a row summed by a butterfly over its lanes
   // (strides 1, 2, 4, ...); four rows per lane group in flight. A sketch wider than 256 gives a
   // lane a second chunk (c + 32), added last.
-  {
+  if (S <= 8) {
+    sketch_rows<1>(cand, n, a.sketch, S, sc, qv, dist);
+  } else if (S <= 16) {
+    sketch_rows<2>(cand, n, a.sketch, S, sc, qv, dist);
+  } else if (S <= 32) {
+    sketch_rows<4>(cand, n, a.sketch, S, sc, qv, dist);
+  } else if (S <= 64) {
+    sketch_rows<8>(cand, n, a.sketch, S, sc, qv, dist);
+  } else if (S <= 128) {
+    sketch_rows<16>(cand, n, a.sketch, S, sc, qv, dist);
+  } else if (S <= 256) {
+    sketch_rows<32>(cand, n, a.sketch, S, sc, qv, dist);
+  } else {
+    // wider than 256: a lane takes a second chunk (c + 32), added last
     const int chunks = S / 8;
     int Lw           = 1;
     while (Lw < chunks && Lw < 32)

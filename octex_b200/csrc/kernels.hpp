@@ -16,12 +16,13 @@ constexpr int kMaxSketchKO = 1024;   // kept entries when ranking by sketch
 constexpr int kMaxExpanded = 6144;   // start points expanded by earlier waves
 constexpr int kRoundThreads = 128;
 
-/// Slots of the hash set that collects `total` entries: at most three quarters full, a multiple of
-/// four, between kMinHash and cap. (The reference, search_kernels.cuh:33-38, takes a power of two at
-/// most two thirds full; only the memory taken differs.)
-__host__ __device__ inline int hash_slots_of(int total, int cap)
+/// Slots of the hash set that collects `total` entries: twelfths / 12 slots per entry (24 = half
+/// full at most, 16 = three quarters), a multiple of four, between kMinHash and cap. (The reference,
+/// search_kernels.cuh:33-38, takes a power of two at most two thirds full; only the memory taken and
+/// the length of the probe sequences differ.)
+__host__ __device__ inline int hash_slots_of(int total, int cap, int twelfths)
 {
-  int need = ((4 * total + 2) / 3 + 3) & ~3;
+  int need = ((twelfths * total + 11) / 12 + 3) & ~3;
   if (need < kMinHash) need = kMinHash;
   return need < cap ? need : cap;
 }
@@ -107,6 +108,7 @@ struct round_args {
   // sizes of the shared-memory carve-up (host decides)
   int ht_slots = 0;   // ints of the hash set region (>= largest set used, >= pick_slots)
   int cap_slots = 0;  // largest gather hash set (slots)
+  int hash_twelfths = 16;  // slots per 12 gathered entries (host: as sparse as shared memory allows)
   int nmax = 0;       // capacity of the candidate / distance arrays
   int P = 0;          // keys sorted by the merge (power of two >= KO)
   int* cand_global = nullptr;    // [m, nmax] when the candidates do not fit shared memory

@@ -548,6 +548,10 @@ __global__ void __launch_bounds__(kRoundThreads, 8) round_kernel(const round_arg
           const int v            = kid[i];
           st[at]                 = v;
           pdone[a.done_off + at] = v;
+          // its table row is read next: start bringing it into L2
+          const char* row = reinterpret_cast<const char*>(a.table + static_cast<int64_t>(v) * a.table_len);
+          for (int b = 0; b < a.table_len * 4; b += 128)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(row + b));
         }
         at++;
       }
@@ -565,6 +569,11 @@ __global__ void __launch_bounds__(kRoundThreads, 8) round_kernel(const round_arg
       st[c]         = sl.x;
       len[c]        = sl.y;
       mine += sl.y;
+      if (sl.y > 0) {  // the run of list entries is read next: start bringing it into L2
+        const char* run = reinterpret_cast<const char*>(a.lists + static_cast<int64_t>(c) * a.stride + sl.x);
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(run));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(run + sl.y * 4 - 4));
+      }
     }
     block_scan(mine, wsum, total);
   }
@@ -573,7 +582,7 @@ __global__ void __launch_bounds__(kRoundThreads, 8) round_kernel(const round_arg
   // threads walks one segment, so consecutive threads read consecutive entries, and every thread
   // has four segments' loads in flight before it touches the set
   tick(0);
-  const int HT = hash_slots_of(total, a.cap_slots);
+  const int HT = hash_slots_of(total, a.cap_slots, a.hash_twelfths);
   for (int i = threadIdx.x; i < HT / 4; i += blockDim.x)
     reinterpret_cast<int4*>(table)[i] = make_int4(-1, -1, -1, -1);
   __syncthreads();

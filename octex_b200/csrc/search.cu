@@ -33,7 +33,6 @@ constexpr size_t kSmemHardLimit = size_t{227} << 10;  // shared memory a block c
 /// Fill the size fields of a round and decide where its candidate arrays live.
 void size_round(plan& pl, kernels::round_args& r, int entries_max, int pick_entries, int device)
 {
-  r.cap_slots  = kernels::hash_slots_of(std::min(entries_max, kernels::kMaxHash), kernels::kMaxHash);
   r.pick_slots = 0;
   if (pick_entries > 0) {
     r.pick_slots = 64;
@@ -43,13 +42,21 @@ void size_round(plan& pl, kernels::round_args& r, int entries_max, int pick_entr
   int kept_slots = 64;  // the set of kept ids a round filters its selection with
   while (kept_slots < 2 * r.KO)
     kept_slots <<= 1;
-  r.ht_slots = std::max({r.cap_slots, r.pick_slots, kept_slots});
-  r.nmax     = std::max(entries_max, 1);
-  r.P = 2;
+  r.nmax = std::max(entries_max, 1);
+  r.P    = 2;
   while (r.P < r.KO)
     r.P <<= 1;
   r.cand_global = nullptr;
   r.dist_global = nullptr;
+  // the gather's hash set: half full at most when eight blocks still fit a multiprocessor's shared
+  // memory (1 KB per block is the system's), else two thirds, else three quarters
+  constexpr size_t kEightBlocks = (size_t{228} << 10) / 8 - 1024;
+  for (int twelfths : {24, 18, 16}) {
+    r.hash_twelfths = twelfths;
+    r.cap_slots = kernels::hash_slots_of(std::min(entries_max, kernels::kMaxHash), kernels::kMaxHash, twelfths);
+    r.ht_slots  = std::max({r.cap_slots, r.pick_slots, kept_slots});
+    if (kernels::round_smem_bytes(r) <= kEightBlocks) break;
+  }
   if (kernels::round_smem_bytes(r) > kSmemSoftLimit) {
     // placeholders: non-null makes the layout drop the two arrays; the real buffers follow
     r.cand_global = reinterpret_cast<int*>(1);

@@ -14,6 +14,7 @@
 
 #include "kernels.hpp"
 
+#include <algorithm>
 #include <cfloat>
 #include <cmath>
 
@@ -42,9 +43,10 @@ struct round_layout {
     // set there again, starts after the selection has copied out the distances it needs). The keys of
     // the merge are written where the candidates were (dead after the selection).
     const int pool_words = 2 * (a.KO + rm);
+    const int sort_words = a.P > 32 ? 4 * a.P : 128;  // 2 P keys, 64 at least (the one-warp sort)
     table  = take(a.ht_slots > in_smem ? a.ht_slots : in_smem);
     dist   = table;
-    cand   = take(in_smem > pool_words + 4 * a.P ? in_smem : pool_words + 4 * a.P);
+    cand   = take(in_smem > pool_words + sort_words ? in_smem : pool_words + sort_words);
     pool   = cand;
     sorted = cand + pool_words;
     sid    = take(rm);
@@ -125,6 +127,40 @@ __device__ __forceinline__ void bitonic_sort(unsigned long long* key, int P)
       __syncthreads();
     }
   }
+}
+
+/// Ascending sort of 64 keys in shared memory by one warp (the caller's warp 0), two keys per lane
+/// in registers: element e = lane + 32 r. The same network as bitonic_sort, without block barriers.
+/// The other warps wait at the caller's next barrier.
+__device__ __forceinline__ void warp_sort64(unsigned long long* key)
+{
+  const int lane = threadIdx.x & 31;
+  unsigned long long k[2] = {key[lane], key[lane + 32]};
+#pragma unroll
+  for (int size = 2; size <= 64; size <<= 1) {
+#pragma unroll
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      if (stride == 32) {
+        // partners sit in the same lane; size is 64 here, so the order is ascending
+        const unsigned long long lo = k[0] < k[1] ? k[0] : k[1], hi = k[0] < k[1] ? k[1] : k[0];
+        k[0] = lo;
+        k[1] = hi;
+      } else {
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+          const int e                  = lane + 32 * r;
+          const unsigned long long o   = __shfl_xor_sync(0xffffffffu, k[r], stride);
+          const bool up                = (e & size) == 0;
+          const bool lower             = (lane & stride) == 0;  // this lane holds the lower index of the pair
+          const bool take_min          = up == lower;
+          const unsigned long long mn  = k[r] < o ? k[r] : o, mx = k[r] < o ? o : k[r];
+          k[r] = take_min ? mn : mx;
+        }
+      }
+    }
+  }
+  key[lane]      = k[0];
+  key[lane + 32] = k[1];
 }
 
 struct radix_cut_t {
@@ -413,7 +449,7 @@ __device__ __forceinline__ void merge_into_kept(unsigned long long* pool,
   if (total <= 2 * P) {
     while (width < total)
       width <<= 1;
-    for (int i = threadIdx.x; i < width; i += blockDim.x)
+    for (int i = threadIdx.x; i < max(width, 64); i += blockDim.x)
       sorted[i] = i < total ? pool[i] : kNoKey;
   } else {
     auto key_at         = [&](int i) { return pool[i]; };
@@ -427,11 +463,16 @@ __device__ __forceinline__ void merge_into_kept(unsigned long long* pool,
         if (s < P) sorted[s] = k;
       }
     }
-    for (int i = KO + threadIdx.x; i < P; i += blockDim.x)
+    for (int i = KO + threadIdx.x; i < max(P, 64); i += blockDim.x)
       sorted[i] = kNoKey;
   }
   __syncthreads();
-  bitonic_sort(sorted, width);
+  if (width <= 64) {  // short lists: one warp sorts 64 keys in registers, no barrier per step
+    if (threadIdx.x < 32) warp_sort64(sorted);
+    __syncthreads();
+  } else {
+    bitonic_sort(sorted, width);
+  }
   for (int i = threadIdx.x; i < KO; i += blockDim.x) {
     const unsigned long long k = i < cnt ? sorted[i] : kNoKey;
     pb[i] = k == kNoKey ? -1 : static_cast<long long>(static_cast<unsigned>(k & 0xffffffffULL));
@@ -846,7 +887,7 @@ __global__ void __launch_bounds__(kRoundThreads) final_rerank_kernel(const long 
   extern __shared__ __align__(16) int smem[];
   unsigned long long* pool   = reinterpret_cast<unsigned long long*>(smem);  // [k + R]
   unsigned long long* sorted = pool + ((k + R + 1) & ~1);                    // [P]
-  int* sid                   = reinterpret_cast<int*>(sorted + 2 * P);       // sorted [2 P]; sid [R]
+  int* sid                   = reinterpret_cast<int*>(sorted + max(2 * P, 64));  // sorted [max(2 P, 64)]; sid [R]
   float* sdv                 = reinterpret_cast<float*>(sid + ((R + 3) & ~3));
   float* fq                  = sdv + ((R + 3) & ~3);                         // [D]
   unsigned* hist             = reinterpret_cast<unsigned*>(fq + ((D + 3) & ~3));
@@ -959,7 +1000,7 @@ void final_rerank(const long long* si, int KO, int R, const __half* vectors, int
   int P = 2;
   while (P < k)
     P <<= 1;
-  const size_t words = 2 * static_cast<size_t>((k + R + 1) & ~1) + 4 * static_cast<size_t>(P) +
+  const size_t words = 2 * static_cast<size_t>((k + R + 1) & ~1) + 2 * static_cast<size_t>(std::max(2 * P, 64)) +
                        2 * static_cast<size_t>((R + 3) & ~3) + ((D + 3) & ~3) + 256 + 16 + 8;
   final_rerank_kernel<<<m, kRoundThreads, sizeof(int) * words, s>>>(si, KO, R, vectors, D, Q, k, P, bi,
                                                                     bd, stats);

@@ -57,6 +57,12 @@ LADDER = [
 ]
 
 
+# DRAM bytes (read + write) of one launch, from the ncu capture of this bench at its default workload
+# and the first rung of LADDER (profiles/round_kernel_descriptor-1m.md). Reported as
+# roofline.traffic only when the run uses exactly that workload and those parameters.
+NCU_TRAFFIC = {"round_rows": 1.240e9, "round_lists": 0.681e9}
+
+
 def log(*a):
     print(*a, file=sys.stderr, flush=True)
 
@@ -330,8 +336,9 @@ def main():
     timed = {k_: v for k_, v in kernel_ms.items() if k_ in alg}
     top = max(timed, key=lambda k_: timed[k_] * launches_per_step.get(k_, 1))
     achieved = alg[top] / (kernel_ms[top] * 1e-3) / 1e9
+    captured = (args.workload == "descriptor-1m" and not args.copies and sp == LADDER[0])
     roofline = {"bound": "hbm", "kernel": top, "achieved": achieved, "peak": peak, "unit": "GB/s",
-                "frac": achieved / peak, "traffic": None,
+                "frac": achieved / peak, "traffic": NCU_TRAFFIC.get(top) if captured else None,
                 "peak_source": "MEASURED_PEAKS.json" if peaks else "fallback 6650 GB/s",
                 "algorithmic_bytes_per_launch": alg[top], "ms_per_launch": kernel_ms[top],
                 "kernel_ms": kernel_ms,

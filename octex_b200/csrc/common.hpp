@@ -57,6 +57,10 @@ struct dbuf {
   ~dbuf()
   {
     if (ptr == nullptr || !owned) return;
+    if (host) {
+      cudaFreeHost(ptr);
+      return;
+    }
     int cur = 0;
     cudaGetDevice(&cur);
     cudaSetDevice(device);
@@ -69,6 +73,19 @@ struct dbuf {
     std::swap(size, o.size);
     std::swap(device, o.device);
     std::swap(owned, o.owned);
+    std::swap(host, o.host);
+  }
+  /// Page-locked host memory every GPU can read through the same pointer (the host tier of an
+  /// index array: cpp/src/neighbors/octex/detail/index_impl.hpp:69-113 of the reference).
+  static auto pinned(int dev, size_t bytes) -> dbuf
+  {
+    dbuf b;
+    b.size   = bytes;
+    b.device = dev;
+    b.host   = true;
+    if (bytes != 0)
+      OCTEX_CUDA_TRY(cudaHostAlloc(&b.ptr, bytes, cudaHostAllocMapped | cudaHostAllocPortable));
+    return b;
   }
   /// A view of memory owned by the caller (arrays attached without a copy).
   static auto borrow(int dev, const void* p, size_t bytes) -> dbuf
@@ -86,6 +103,7 @@ struct dbuf {
     return static_cast<T*>(ptr);
   }
   bool owned = true;
+  bool host  = false;
 };
 
 }  // namespace octex_b200

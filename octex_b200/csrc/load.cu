@@ -118,10 +118,6 @@ void place(index_impl& ix, source_arrays const& src)
                 "octex: blocks must be 1-6 or 8");
   OCTEX_EXPECTS(L >= 1 && L <= 16, "octex: 1 to 16 spacings");
   OCTEX_EXPECTS(ix.log_buckets >= 1 && ix.log_buckets <= 30, "octex: log_buckets in [1, 30]");
-  OCTEX_EXPECTS(!params.vectors_on_host && !params.table_on_host &&
-                  params.sketch != sketch_placement::host,
-                "octex: host-memory tiers (vectors_on_host, table_on_host, sketch=host) are not "
-                "available in this build");
   OCTEX_EXPECTS(!params.shard_vectors && params.sketch != sketch_placement::shard,
                 "octex: row-sharded vectors and sketch are not available in this build");
   OCTEX_EXPECTS(ix.world >= 1 && ix.rank >= 0 && ix.rank < ix.world, "octex: rank outside world");
@@ -195,6 +191,13 @@ void place(index_impl& ix, source_arrays const& src)
     own(dst, bytes);
     st.copy(dst.ptr, srcp, bytes);
   };
+  // the host tier (load.cu:328-330): the array lives in page-locked host memory and the kernels
+  // read it over the bus through the same pointer; it does not count as device memory
+  auto put_rows_host = [&](dbuf& dst, const void* srcp, size_t bytes) {
+    dst = dbuf::pinned(p.device, bytes);
+    OCTEX_CUDA_TRY(cudaMemcpyAsync(dst.ptr, srcp, bytes, cudaMemcpyDefault, p.stream));
+    OCTEX_CUDA_TRY(cudaStreamSynchronize(p.stream));
+  };
 
   // lists: the first ll entries of every cell row (load.cu:361-379)
   const int64_t stride0 = a.stride;
@@ -265,11 +268,20 @@ void place(index_impl& ix, source_arrays const& src)
   st.copy(p.basis.ptr, a.basis, p.basis.size);
   own(p.scale, S * sizeof(float));
   st.copy(p.scale.ptr, a.scale, p.scale.size);
-  put_rows(p.sketch, a.sketch, static_cast<size_t>(N * S));
-  put_rows(p.vectors, a.vectors, static_cast<size_t>(N * D) * sizeof(__half));
+  if (params.sketch == sketch_placement::host)
+    put_rows_host(p.sketch, a.sketch, static_cast<size_t>(N * S));
+  else
+    put_rows(p.sketch, a.sketch, static_cast<size_t>(N * S));
+  if (params.vectors_on_host)
+    put_rows_host(p.vectors, a.vectors, static_cast<size_t>(N * D) * sizeof(__half));
+  else
+    put_rows(p.vectors, a.vectors, static_cast<size_t>(N * D) * sizeof(__half));
   if (ix.table_len > 0) {
     OCTEX_EXPECTS(a.table != nullptr, "octex: table_len > 0 without a table");
-    put_rows(p.table, a.table, static_cast<size_t>(N * ix.table_len) * sizeof(int32_t));
+    if (params.table_on_host)
+      put_rows_host(p.table, a.table, static_cast<size_t>(N * ix.table_len) * sizeof(int32_t));
+    else
+      put_rows(p.table, a.table, static_cast<size_t>(N * ix.table_len) * sizeof(int32_t));
   }
   OCTEX_CUDA_TRY(cudaStreamSynchronize(p.stream));
   ix.list_len = ll;

@@ -242,8 +242,23 @@ def test_directory_load_equals_attach(oracle, small_index, gpu_small, tmp_path):
     want_i, want_d, _ = oracle.Index(cut, cmeta).search(queries, 10, read=8, starts=32, waves=1)
     assert np.array_equal(i2, want_i) and np.array_equal(d2.view(np.uint32), want_d.view(np.uint32))
     idx.close()
-    with pytest.raises(ValueError, match="host-memory tiers"):
-        octex_b200.load(path, placement="replicate", vectors_on_host=True)
+    # host tiers (load.cu:328-330): arrays in page-locked host memory read through the same pointer;
+    # same results, less device memory
+    full_bytes = None
+    for tiers in (dict(), dict(vectors_on_host=True), dict(table_on_host=True), dict(sketch="host"),
+                  dict(vectors_on_host=True, table_on_host=True, sketch="host")):
+        idx = octex_b200.load(path, placement="replicate", **tiers)
+        for kw2 in (kw, dict(read=8, starts=16, waves=2, sketch_rank=True, final_rerank=32)):
+            d3, i3 = idx.search(queries, 10, **kw2)
+            d4, i4 = gpu_small[0].search(queries, 10, **kw2)
+            assert np.array_equal(i3, i4) and np.array_equal(d3, d4), tiers
+        if not tiers:
+            full_bytes = idx.device_bytes[0]
+        else:
+            assert idx.device_bytes[0] < full_bytes, tiers
+        idx.close()
+    with pytest.raises(ValueError, match="row-sharded"):
+        octex_b200.load(path, placement="replicate", shard_vectors=True)
     with pytest.raises(ValueError, match="holds no copies"):
         octex_b200.load(path, placement="shard", rank=0, world=64)
 

@@ -446,10 +446,13 @@ cuvsError_t octexB200CommInit(cuvsOctexIndex_t index, const void* id128)
     OCTEX_EXPECTS(id128 != nullptr, "octex: a NULL id buffer");
     auto& ix = as_index(*index)->impl();
     OCTEX_EXPECTS(ix.world > 1, "octex: the index belongs to a single process");
-    std::lock_guard<std::mutex> lock(ix.mu);
-    ix.plans.clear();
-    ix.comm = std::make_unique<octex_b200::detail::communicator>(id128, ix.rank, ix.world,
-                                                                 ix.part.device);
+    {
+      std::lock_guard<std::mutex> lock(ix.mu);
+      ix.plans.clear();
+      ix.comm = std::make_unique<octex_b200::detail::communicator>(id128, ix.rank, ix.world,
+                                                                   ix.part.device);
+    }
+    octex_b200::detail::connect_rows(ix);  // arrays dealt by rows: map the other processes' ranges
   });
 }
 

@@ -40,6 +40,17 @@ struct debug_options {
   bool ordered_projection = false;
 };
 
+/// An array whose rows are dealt over the processes in ranges of rows_per (load.cu:315,406-427 of
+/// the reference): this process holds rows [row0, row0 + own rows) in `mine`; after the processes
+/// are connected, `ptrs` (device, one pointer per process) gives every range's address, the other
+/// processes' memory being mapped into this one.
+struct dealt_rows {
+  bool on          = false;
+  int64_t rows_per = 0, row0 = 0;
+  dbuf ptrs;                  // long long [world], null until connected
+  std::vector<void*> opened;  // mappings of other processes' memory, closed with the index
+};
+
 struct device_part {
   int device     = 0;
   int copies     = 0;  // copies held by this process
@@ -49,6 +60,7 @@ struct device_part {
   int ldu        = 0;
   dbuf lists, keys, offsets, base, ut, shift, inv_f, mean, basis, scale, sketch, vectors, table,
     level_on;
+  dealt_rows table_rows, sketch_rows, vector_rows;
   cudaStream_t stream = nullptr;
   int64_t bytes       = 0;
 
@@ -56,13 +68,16 @@ struct device_part {
   device_part(device_part const&) = delete;
   ~device_part()
   {
-    if (stream != nullptr) {
-      int cur = 0;
-      cudaGetDevice(&cur);
-      cudaSetDevice(device);
-      cudaStreamDestroy(stream);
-      cudaSetDevice(cur);
-    }
+    int cur = 0;
+    cudaGetDevice(&cur);
+    cudaSetDevice(device);
+    // nothing of this process reads the other processes' memory any more (a search returns after
+    // every process has sent its results, so none of them is still reading this one's either)
+    for (dealt_rows* d : {&table_rows, &sketch_rows, &vector_rows})
+      for (void* p : d->opened)
+        cudaIpcCloseMemHandle(p);
+    if (stream != nullptr) cudaStreamDestroy(stream);
+    cudaSetDevice(cur);
   }
 };
 
@@ -90,5 +105,8 @@ struct source_arrays {
 };
 
 void place(index_impl& ix, source_arrays const& src);
+/// After the communicator exists: exchange the addresses of the row ranges dealt over the
+/// processes (a collective: every process calls it).
+void connect_rows(index_impl& ix);
 
 }  // namespace octex_b200::detail

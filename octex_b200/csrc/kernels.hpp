@@ -73,6 +73,16 @@ void probe(const long long* codes, int m, int C, int L, const int* offsets, int6
            const long long* keys, int64_t mmax, const int* base, const unsigned char* level_on,
            int list_len, int lr, int log_buckets, int2* seg, long long* stats, cudaStream_t s);
 
+/// Where the rows of an array live when they are dealt over the GPUs in ranges of `rows`
+/// (ptrs[g] = start of rows [g * rows, (g + 1) * rows) in that GPU's memory, mapped into this
+/// process); ptrs == nullptr: the whole array is behind the plain pointer. The reference's
+/// xptr / cptr / tptr tables with xrows / crows (detail/search_kernels.cuh:40-55).
+struct row_map {
+  const long long* ptrs = nullptr;
+  int rows              = 0;
+  int local             = 0;  // a row this GPU holds itself (stand-in where a lane has no row to read)
+};
+
 /// One round of a query block: distinct ids of its segments, sketch distances, the R nearest by
 /// sketch reranked exactly (or the KO nearest kept by sketch distance), merged into the kept list.
 struct round_args {
@@ -113,6 +123,8 @@ struct round_args {
   int P = 0;          // keys sorted by the merge (power of two >= KO)
   int* cand_global = nullptr;    // [m, nmax] when the candidates do not fit shared memory
   float* dist_global = nullptr;  // [m, nmax]
+  // rows dealt over GPUs (all empty: every array is whole behind its pointer)
+  row_map table_map, sketch_map, vector_map;
   // observation (all may be null)
   int* tap_cand = nullptr;    // [m, tap_cap]
   float* tap_dist = nullptr;  // [m, tap_cap]
@@ -135,8 +147,9 @@ void take_k(const long long* si, const float* sd, int KO, int k, int m, long lon
             cudaStream_t s);
 
 /// Exact rerank of the first R kept entries (sketch ranking) into the best k.
-void final_rerank(const long long* si, int KO, int R, const __half* vectors, int D, const float* Q,
-                  int k, int m, long long* bi, float* bd, long long* stats, cudaStream_t s);
+void final_rerank(const long long* si, int KO, int R, const __half* vectors, row_map vector_map, int D,
+                  const float* Q, int k, int m, long long* bi, float* bd, long long* stats,
+                  cudaStream_t s);
 
 /// Merge of nsrc kept lists [*, KO] (already in this GPU's memory, back to back: source h at
 /// src + h * src_stride): nearest copy of every id, best KO.

@@ -118,8 +118,6 @@ void place(index_impl& ix, source_arrays const& src)
                 "octex: blocks must be 1-6 or 8");
   OCTEX_EXPECTS(L >= 1 && L <= 16, "octex: 1 to 16 spacings");
   OCTEX_EXPECTS(ix.log_buckets >= 1 && ix.log_buckets <= 30, "octex: log_buckets in [1, 30]");
-  OCTEX_EXPECTS(!params.shard_vectors && params.sketch != sketch_placement::shard,
-                "octex: row-sharded vectors and sketch are not available in this build");
   OCTEX_EXPECTS(ix.world >= 1 && ix.rank >= 0 && ix.rank < ix.world, "octex: rank outside world");
 
   // copies of this process (load.cu:252-281)
@@ -268,23 +266,90 @@ void place(index_impl& ix, source_arrays const& src)
   st.copy(p.basis.ptr, a.basis, p.basis.size);
   own(p.scale, S * sizeof(float));
   st.copy(p.scale.ptr, a.scale, p.scale.size);
+  // rows dealt over the processes (load.cu:315,406-427): this process keeps rows
+  // [rank * rows_per, (rank + 1) * rows_per) in memory of its own; the other ranges are mapped in
+  // when the processes connect. With one process every array is whole.
+  const int64_t rows_per = (N + ix.world - 1) / ix.world;
+  auto put_rows_dealt    = [&](dbuf& dst, dealt_rows& d, const void* srcp, size_t row_bytes) {
+    d.on             = true;
+    d.rows_per       = rows_per;
+    d.row0           = std::min<int64_t>(N, ix.rank * rows_per);
+    const int64_t r1 = std::min<int64_t>(N, d.row0 + rows_per);
+    own(dst, static_cast<size_t>(r1 - d.row0) * row_bytes);
+    st.copy(dst.ptr, static_cast<const char*>(srcp) + d.row0 * row_bytes, dst.size);
+  };
+  const bool many = ix.world > 1;
   if (params.sketch == sketch_placement::host)
     put_rows_host(p.sketch, a.sketch, static_cast<size_t>(N * S));
+  else if (params.sketch == sketch_placement::shard && many)
+    put_rows_dealt(p.sketch, p.sketch_rows, a.sketch, static_cast<size_t>(S));
   else
     put_rows(p.sketch, a.sketch, static_cast<size_t>(N * S));
   if (params.vectors_on_host)
     put_rows_host(p.vectors, a.vectors, static_cast<size_t>(N * D) * sizeof(__half));
+  else if (params.shard_vectors && many)
+    put_rows_dealt(p.vectors, p.vector_rows, a.vectors, static_cast<size_t>(D) * sizeof(__half));
   else
     put_rows(p.vectors, a.vectors, static_cast<size_t>(N * D) * sizeof(__half));
   if (ix.table_len > 0) {
     OCTEX_EXPECTS(a.table != nullptr, "octex: table_len > 0 without a table");
     if (params.table_on_host)
       put_rows_host(p.table, a.table, static_cast<size_t>(N * ix.table_len) * sizeof(int32_t));
+    else if (shard)  // shard placement always deals the table (load.cu:421-427)
+      put_rows_dealt(p.table, p.table_rows, a.table, static_cast<size_t>(ix.table_len) * sizeof(int32_t));
     else
       put_rows(p.table, a.table, static_cast<size_t>(N * ix.table_len) * sizeof(int32_t));
   }
   OCTEX_CUDA_TRY(cudaStreamSynchronize(p.stream));
   ix.list_len = ll;
+}
+
+/// Once the processes have a communicator: every process publishes the address of the row ranges
+/// it holds and maps the other processes' ranges into its own address space (CUDA IPC handles,
+/// exchanged with an all-gather); the kernels then read a row wherever it lives with plain loads,
+/// as the reference's kernels do through its xptr / cptr / tptr tables (load.cu:187-202,444-490).
+void connect_rows(index_impl& ix)
+{
+  auto& p = ix.part;
+  if (ix.world <= 1 || ix.comm == nullptr) return;
+  OCTEX_CUDA_TRY(cudaSetDevice(p.device));
+  struct item {
+    dealt_rows* d;
+    dbuf* mine;
+  };
+  const item items[] = {{&p.table_rows, &p.table}, {&p.sketch_rows, &p.sketch}, {&p.vector_rows, &p.vectors}};
+  const size_t hb = sizeof(cudaIpcMemHandle_t);
+  dbuf send(p.device, hb), recv(p.device, hb * ix.world);
+  for (auto const& it : items) {
+    auto& d = *it.d;
+    if (!d.on || d.ptrs.ptr != nullptr) continue;
+    cudaIpcMemHandle_t h{};
+    if (it.mine->size != 0) OCTEX_CUDA_TRY(cudaIpcGetMemHandle(&h, it.mine->ptr));
+    OCTEX_CUDA_TRY(cudaMemcpyAsync(send.ptr, &h, hb, cudaMemcpyHostToDevice, p.stream));
+    ix.comm->all_gather(send.ptr, recv.ptr, hb, p.stream);
+    std::vector<cudaIpcMemHandle_t> all(ix.world);
+    OCTEX_CUDA_TRY(cudaMemcpyAsync(all.data(), recv.ptr, hb * ix.world, cudaMemcpyDeviceToHost, p.stream));
+    OCTEX_CUDA_TRY(cudaStreamSynchronize(p.stream));
+    std::vector<long long> ptrs(ix.world, 0);
+    for (int g = 0; g < ix.world; g++) {
+      const int64_t r0 = std::min<int64_t>(ix.n, g * d.rows_per);
+      const int64_t r1 = std::min<int64_t>(ix.n, r0 + d.rows_per);
+      if (r1 <= r0) continue;  // that process holds no rows
+      if (g == ix.rank) {
+        ptrs[g] = reinterpret_cast<long long>(it.mine->ptr);
+      } else {
+        void* q = nullptr;
+        OCTEX_CUDA_TRY(cudaIpcOpenMemHandle(&q, all[g], cudaIpcMemLazyEnablePeerAccess));
+        d.opened.push_back(q);
+        ptrs[g] = reinterpret_cast<long long>(q);
+      }
+    }
+    d.ptrs = dbuf(p.device, sizeof(long long) * ix.world);
+    OCTEX_CUDA_TRY(cudaMemcpyAsync(d.ptrs.ptr, ptrs.data(), d.ptrs.size, cudaMemcpyHostToDevice, p.stream));
+    OCTEX_CUDA_TRY(cudaStreamSynchronize(p.stream));
+  }
+  std::lock_guard<std::mutex> lock(ix.mu);
+  ix.plans.clear();  // plans made before the connection do not know the tables
 }
 
 }  // namespace detail

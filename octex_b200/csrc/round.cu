@@ -245,15 +245,37 @@ __device__ __forceinline__ float sketch_chunk8(uint2 w, const float* s, const fl
   return d;
 }
 
+/// Row `id` of an array with `width` elements per row: behind `base`, or (kDealt and a table given)
+/// in the memory of the GPU that holds its range (search_kernels.cuh:40-55).
+template <bool kDealt, typename T>
+__device__ __forceinline__ const T* row_of(const T* base, const row_map& m, int id, int width)
+{
+  if constexpr (kDealt) {
+    if (m.ptrs != nullptr) {
+      const int g = id / m.rows;
+      return reinterpret_cast<const T*>(m.ptrs[g]) + static_cast<int64_t>(id - g * m.rows) * width;
+    }
+  }
+  return base + static_cast<int64_t>(id) * width;
+}
+
+/// Rows that may sit in another GPU's memory are not prefetched into this GPU's L2.
+template <bool kDealt>
+__device__ __forceinline__ bool may_prefetch(const row_map& m)
+{
+  return !kDealt || m.ptrs == nullptr;
+}
+
 /// Sketch distances of the candidates cand[0, n) into dist[0, n) for a sketch of at most 32 chunks
 /// of eight codes: kLw (a power of two >= chunks) lanes own a row, one chunk each with its scale
 /// and query coordinates in registers; the chunk sums of a row are added by a butterfly over its
 /// lanes (strides 1, 2, 4, ...); a lane group has four rows in flight. Straight-line code: a lane
 /// past the last row or past the last chunk works on a valid stand-in and its result is dropped
 /// (a chunk past the end has scale and query 0, so it adds exactly 0).
-template <int kLw>
+template <int kLw, bool kDealt>
 __device__ __forceinline__ void sketch_rows(const int* cand, int n, const signed char* __restrict__ sketch,
-                                            int S, const float* sc, const float* qv, float* dist)
+                                            const row_map& map, int S, const float* sc, const float* qv,
+                                            float* dist)
 {
   constexpr int kG = 32 / kLw;  // rows per warp and step
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
@@ -275,7 +297,7 @@ __device__ __forceinline__ void sketch_rows(const int* cand, int n, const signed
     for (int u = 0; u < 4; u++) {
       j[u]         = jb + u * rpp + warp * kG + grp;
       const int id = cand[min(j[u], n - 1)];
-      w[u] = __ldg(reinterpret_cast<const uint2*>(sketch + static_cast<int64_t>(id) * S) + subc);
+      w[u] = __ldg(reinterpret_cast<const uint2*>(row_of<kDealt>(sketch, map, id, S)) + subc);
     }
 #pragma unroll
     for (int u = 0; u < 4; u++) {
@@ -348,8 +370,9 @@ __device__ __forceinline__ void exact_pair(const uint4* const (&row)[2], int D, 
 /// 1, 2, 4, 8, 16 (search_kernels.cuh:325-342 is the reference's warp-per-row form of the same
 /// sum). Eight lanes own a row, each reading 16 bytes per step (partial sums 4 lane .. 4 lane + 3);
 /// a warp works on eight rows at a time.
-__device__ __forceinline__ void exact_distances(
-  const int* sid, int ns, const __half* __restrict__ vectors, int D, const float* fq, float* sdv)
+template <bool kDealt>
+__device__ __forceinline__ void exact_distances(const int* sid, int ns, const __half* __restrict__ vectors,
+                                                const row_map& map, int D, const float* fq, float* sdv)
 {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   if ((D & 7) == 0) {
@@ -363,8 +386,9 @@ __device__ __forceinline__ void exact_distances(
         j[u]         = jb + u * nw * 4 + warp * 4 + grp;
         const int id = j[u] < ns ? sid[j[u]] : -1;
         wanted[u]    = id >= 0;
-        // a slot without a row works on row 0 (cached after its first use) and drops the result
-        row[u] = reinterpret_cast<const uint4*>(vectors + static_cast<int64_t>(wanted[u] ? id : 0) * D);
+        // a slot without a row works on a row this GPU holds (cached after its first use) and drops
+        // the result
+        row[u] = reinterpret_cast<const uint4*>(row_of<kDealt>(vectors, map, wanted[u] ? id : map.local, D));
       }
       float out[2];
       if ((D & 127) == 0)
@@ -378,7 +402,7 @@ __device__ __forceinline__ void exact_distances(
   } else {
     for (int j = warp; j < ns; j += nw) {
       if (sid[j] < 0) continue;
-      const __half2* row = reinterpret_cast<const __half2*>(vectors + static_cast<int64_t>(sid[j]) * D);
+      const __half2* row = reinterpret_cast<const __half2*>(row_of<kDealt>(vectors, map, sid[j], D));
       float acc          = 0.f;
       for (int k = lane; k < D / 2; k += 32) {
         const float2 x = __half22float2(row[k]);
@@ -481,7 +505,7 @@ __device__ __forceinline__ void merge_into_kept(unsigned long long* pool,
 }
 
 
-template <bool kRows>
+template <bool kRows, bool kDealt>
 __global__ void __launch_bounds__(kRoundThreads, 8) round_kernel(const round_args a)
 {
   extern __shared__ __align__(16) int smem[];
@@ -590,9 +614,11 @@ __global__ void __launch_bounds__(kRoundThreads, 8) round_kernel(const round_arg
           st[at]                 = v;
           pdone[a.done_off + at] = v;
           // its table row is read next: start bringing it into L2
-          const char* row = reinterpret_cast<const char*>(a.table + static_cast<int64_t>(v) * a.table_len);
-          for (int b = 0; b < a.table_len * 4; b += 128)
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(row + b));
+          if (may_prefetch<kDealt>(a.table_map)) {
+            const char* row = reinterpret_cast<const char*>(a.table + static_cast<int64_t>(v) * a.table_len);
+            for (int b = 0; b < a.table_len * 4; b += 128)
+              asm volatile("prefetch.global.L2 [%0];" ::"l"(row + b));
+          }
         }
         at++;
       }
@@ -646,7 +672,7 @@ __global__ void __launch_bounds__(kRoundThreads, 8) round_kernel(const round_arg
           v[u]        = -1;
           if (s < nseg && w0 < maxlen) {
             if constexpr (kRows) {
-              v[u] = __ldg(a.table + static_cast<int64_t>(st[s]) * a.table_len + w0);
+              v[u] = __ldg(row_of<kDealt>(a.table, a.table_map, st[s], a.table_len) + w0);
             } else {
               if (w0 < len[s]) v[u] = __ldg(a.lists + static_cast<int64_t>(s) * a.stride + st[s] + w0);
             }
@@ -664,7 +690,8 @@ __global__ void __launch_bounds__(kRoundThreads, 8) round_kernel(const round_arg
               if (prev == -1) {
                 is_new = true;
                 // the sketch row of a new id will be wanted soon: start bringing it into L2
-                asm volatile("prefetch.global.L2 [%0];" ::"l"(a.sketch + static_cast<int64_t>(id) * S));
+                if (may_prefetch<kDealt>(a.sketch_map))
+                  asm volatile("prefetch.global.L2 [%0];" ::"l"(a.sketch + static_cast<int64_t>(id) * S));
                 break;
               }
               if (prev == id) break;
@@ -704,17 +731,17 @@ __global__ void __launch_bounds__(kRoundThreads, 8) round_kernel(const round_arg
   // (strides 1, 2, 4, ...); four rows per lane group in flight. A sketch wider than 256 gives a
   // lane a second chunk (c + 32), added last.
   if (S <= 8) {
-    sketch_rows<1>(cand, n, a.sketch, S, sc, qv, dist);
+    sketch_rows<1, kDealt>(cand, n, a.sketch, a.sketch_map, S, sc, qv, dist);
   } else if (S <= 16) {
-    sketch_rows<2>(cand, n, a.sketch, S, sc, qv, dist);
+    sketch_rows<2, kDealt>(cand, n, a.sketch, a.sketch_map, S, sc, qv, dist);
   } else if (S <= 32) {
-    sketch_rows<4>(cand, n, a.sketch, S, sc, qv, dist);
+    sketch_rows<4, kDealt>(cand, n, a.sketch, a.sketch_map, S, sc, qv, dist);
   } else if (S <= 64) {
-    sketch_rows<8>(cand, n, a.sketch, S, sc, qv, dist);
+    sketch_rows<8, kDealt>(cand, n, a.sketch, a.sketch_map, S, sc, qv, dist);
   } else if (S <= 128) {
-    sketch_rows<16>(cand, n, a.sketch, S, sc, qv, dist);
+    sketch_rows<16, kDealt>(cand, n, a.sketch, a.sketch_map, S, sc, qv, dist);
   } else if (S <= 256) {
-    sketch_rows<32>(cand, n, a.sketch, S, sc, qv, dist);
+    sketch_rows<32, kDealt>(cand, n, a.sketch, a.sketch_map, S, sc, qv, dist);
   } else {
     // wider than 256: a lane takes a second chunk (c + 32), added last
     const int chunks = S / 8;
@@ -738,7 +765,7 @@ __global__ void __launch_bounds__(kRoundThreads, 8) round_kernel(const round_arg
       for (int u = 0; u < 4; u++) {
         j[u] = jb + u * rpp + warp * G + lane / Lw;
         if (j[u] < n && live)
-          w[u] = __ldg(reinterpret_cast<const uint2*>(a.sketch + static_cast<int64_t>(cand[j[u]]) * S + sub * 8));
+          w[u] = __ldg(reinterpret_cast<const uint2*>(row_of<kDealt>(a.sketch, a.sketch_map, cand[j[u]], S) + sub * 8));
       }
 #pragma unroll
       for (int u = 0; u < 4; u++) {
@@ -749,7 +776,7 @@ __global__ void __launch_bounds__(kRoundThreads, 8) round_kernel(const round_arg
           float e = 0.f;
           if (j[u] < n && live2) {
             const uint2 w2 = __ldg(reinterpret_cast<const uint2*>(
-              a.sketch + static_cast<int64_t>(cand[j[u]]) * S + (sub + 32) * 8));
+              row_of<kDealt>(a.sketch, a.sketch_map, cand[j[u]], S) + (sub + 32) * 8));
             e = sketch_chunk8(w2, sc + (sub + 32) * 8, qv + (sub + 32) * 8);
           }
           for (int o = 1; o < 32; o <<= 1)
@@ -838,7 +865,7 @@ __global__ void __launch_bounds__(kRoundThreads, 8) round_kernel(const round_arg
     // every row about to be read is asked for at once (128-byte lines into L2), so the distance
     // loop below finds most of them on the way
     const int lines = (a.D * 2 + 127) >> 7;
-    for (int i = threadIdx.x; i < ns * lines; i += blockDim.x) {
+    for (int i = threadIdx.x; i < (may_prefetch<kDealt>(a.vector_map) ? ns * lines : 0); i += blockDim.x) {
       const int r = i / lines;
       if (sid[r] < 0) continue;
       asm volatile("prefetch.global.L2 [%0];" ::"l"(
@@ -851,7 +878,7 @@ __global__ void __launch_bounds__(kRoundThreads, 8) round_kernel(const round_arg
       block_scan(mine, wsum, reranked);
     }
     tick(4);
-    exact_distances(sid, ns, a.vectors, a.D, fq, sdv);
+    exact_distances<kDealt>(sid, ns, a.vectors, a.vector_map, a.D, fq, sdv);
     tick(5);
   }
   merge_into_kept(pool, sorted, a.P, pb, pd, a.KO, fresh ? nullptr : kid, kd, sid, sdv, ns, hist, ctrl);
@@ -876,6 +903,7 @@ __global__ void __launch_bounds__(kRoundThreads) final_rerank_kernel(const long 
                                                                      int KO,
                                                                      int R,
                                                                      const __half* __restrict__ vectors,
+                                                                     const row_map vector_map,
                                                                      int D,
                                                                      const float* __restrict__ Q,
                                                                      int k,
@@ -906,7 +934,7 @@ __global__ void __launch_bounds__(kRoundThreads) final_rerank_kernel(const long 
   }
   int ns = 0;
   block_scan(mine, wsum, ns);
-  exact_distances(sid, ns, vectors, D, fq, sdv);
+  exact_distances<true>(sid, ns, vectors, vector_map, D, fq, sdv);
   merge_into_kept(pool, sorted, P, bi + static_cast<int64_t>(q) * k, bd + static_cast<int64_t>(q) * k,
                   k, nullptr, nullptr, sid, sdv, ns, hist, ctrl);
   if (stats != nullptr && threadIdx.x == 0) {
@@ -975,26 +1003,41 @@ size_t round_smem_bytes(const round_args& a) { return sizeof(int) * round_layout
 
 void round_allow_smem(size_t bytes)
 {
-  cudaFuncSetAttribute(round_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                       static_cast<int>(bytes));
-  cudaFuncSetAttribute(round_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                       static_cast<int>(bytes));
+  const int b = static_cast<int>(bytes);
+  cudaFuncSetAttribute(round_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, b);
+  cudaFuncSetAttribute(round_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, b);
+  cudaFuncSetAttribute(round_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, b);
+  cudaFuncSetAttribute(round_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, b);
 }
+
+namespace {
+bool dealt(const round_args& a)
+{
+  return a.table_map.ptrs != nullptr || a.sketch_map.ptrs != nullptr || a.vector_map.ptrs != nullptr;
+}
+}  // namespace
 
 void round_lists(const round_args& a, cudaStream_t s)
 {
   if (a.m <= 0) return;
-  round_kernel<false><<<a.m, kRoundThreads, round_smem_bytes(a), s>>>(a);
+  if (dealt(a))
+    round_kernel<false, true><<<a.m, kRoundThreads, round_smem_bytes(a), s>>>(a);
+  else
+    round_kernel<false, false><<<a.m, kRoundThreads, round_smem_bytes(a), s>>>(a);
 }
 
 void round_rows(const round_args& a, cudaStream_t s)
 {
   if (a.m <= 0) return;
-  round_kernel<true><<<a.m, kRoundThreads, round_smem_bytes(a), s>>>(a);
+  if (dealt(a))
+    round_kernel<true, true><<<a.m, kRoundThreads, round_smem_bytes(a), s>>>(a);
+  else
+    round_kernel<true, false><<<a.m, kRoundThreads, round_smem_bytes(a), s>>>(a);
 }
 
-void final_rerank(const long long* si, int KO, int R, const __half* vectors, int D, const float* Q,
-                  int k, int m, long long* bi, float* bd, long long* stats, cudaStream_t s)
+void final_rerank(const long long* si, int KO, int R, const __half* vectors, row_map vector_map, int D,
+                  const float* Q, int k, int m, long long* bi, float* bd, long long* stats,
+                  cudaStream_t s)
 {
   if (m <= 0) return;
   int P = 2;
@@ -1002,8 +1045,8 @@ void final_rerank(const long long* si, int KO, int R, const __half* vectors, int
     P <<= 1;
   const size_t words = 2 * static_cast<size_t>((k + R + 1) & ~1) + 2 * static_cast<size_t>(std::max(2 * P, 64)) +
                        2 * static_cast<size_t>((R + 3) & ~3) + ((D + 3) & ~3) + 256 + 16 + 8;
-  final_rerank_kernel<<<m, kRoundThreads, sizeof(int) * words, s>>>(si, KO, R, vectors, D, Q, k, P, bi,
-                                                                    bd, stats);
+  final_rerank_kernel<<<m, kRoundThreads, sizeof(int) * words, s>>>(si, KO, R, vectors, vector_map, D, Q,
+                                                                    k, P, bi, bd, stats);
 }
 
 void merge_kept(const long long* src_i, const float* src_d, int nsrc, int64_t src_stride, int KO,

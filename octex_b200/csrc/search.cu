@@ -27,6 +27,21 @@ auto alloc(plan& pl, int device, int64_t count, int fill = -2) -> dbuf
   return b;
 }
 
+/// The kernels' view of an array dealt by rows (empty when the array is whole).
+auto map_of(index_impl const& ix, dealt_rows const& d) -> kernels::row_map
+{
+  kernels::row_map m;
+  if (!d.on) return m;
+  OCTEX_EXPECTS(d.ptrs.ptr != nullptr,
+                "octex: the index holds row ranges of other processes: connect the processes first "
+                "(octexB200CommInit)");
+  OCTEX_EXPECTS(d.rows_per < (int64_t{1} << 31), "octex: more than 2^31 rows per process");
+  m.ptrs  = d.ptrs.as<long long>();
+  m.rows  = static_cast<int>(d.rows_per);
+  m.local = static_cast<int>(std::min<int64_t>(d.row0, ix.n - 1));
+  return m;
+}
+
 constexpr size_t kSmemSoftLimit = size_t{96} << 10;   // above this the candidates go to global memory
 constexpr size_t kSmemHardLimit = size_t{227} << 10;  // shared memory a block can opt in to
 
@@ -184,8 +199,8 @@ void run_batch(index_impl const& ix, plan& pl, cudaStream_t s, std::vector<cudaE
     mark();
   }
   if (pl.sp.sketch_rank && pl.FR > 0) {
-    kernels::final_rerank(pl.wsi, pl.KO, pl.FR, p.vectors.as<__half>(), D, Qw, pl.k, pl.mw,
-                          pl.bi.as<long long>(), pl.bd.as<float>(), pl.stats.as<long long>(), s);
+    kernels::final_rerank(pl.wsi, pl.KO, pl.FR, p.vectors.as<__half>(), pl.r1.vector_map, D, Qw, pl.k,
+                          pl.mw, pl.bi.as<long long>(), pl.bd.as<float>(), pl.stats.as<long long>(), s);
   } else {
     kernels::take_k(pl.wsi, pl.wsd, pl.KO, pl.k, pl.mw, pl.bi.as<long long>(), pl.bd.as<float>(), s);
   }
@@ -360,6 +375,8 @@ auto make_plan(index_impl& ix, search_params const& sp, int m, int k, debug_opti
   r1.R           = pl.R1;
   r1.KO          = pl.KO;
   r1.sketch_rank = sp.sketch_rank ? 1 : 0;
+  r1.sketch_map  = map_of(ix, p.sketch_rows);
+  r1.vector_map  = map_of(ix, p.vector_rows);
   r1.fresh       = 1;
   r1.si          = pl.si.as<long long>();
   r1.sd          = pl.sd.as<float>();
@@ -380,6 +397,9 @@ auto make_plan(index_impl& ix, search_params const& sp, int m, int k, debug_opti
     r2.nseg        = S;
     r2.table       = p.table.as<int>();
     r2.table_len   = ix.table_len;
+    r2.table_map   = map_of(ix, p.table_rows);
+    r2.sketch_map  = r1.sketch_map;
+    r2.vector_map  = r1.vector_map;
     r2.done        = pl.done.as<int>();
     r2.done_stride = S * sp.waves;
     r2.sketch      = r1.sketch;

@@ -1,4 +1,5 @@
-"""Two processes, two GPUs: shard and replicate placement through NCCL, against the CPU checker
+"""Two processes, two GPUs: shard and replicate placement through NCCL, with the row arrays whole,
+dealt over the GPUs (read through mapped peer memory) or in host memory, against the CPU checker
 (sharded first round: `parts=2`).  Skipped with fewer than two GPUs."""
 import os
 import sys
@@ -10,7 +11,7 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def worker(rank, world, port, path, out, placement):
+def worker(rank, world, port, path, out, placement, tiers):
     sys.path.insert(0, ROOT)
     import torch
     import torch.distributed as dist
@@ -19,7 +20,13 @@ def worker(rank, world, port, path, out, placement):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     torch.cuda.set_device(rank)
     dist.init_process_group("gloo", rank=rank, world_size=world)
-    idx = octex_b200.load(path, devices=[rank], placement=placement, rank=rank, world=world)
+    idx = octex_b200.load(path, devices=[rank], placement=placement, rank=rank, world=world, **tiers)
+    # nothing of the other processes is reachable before the processes are connected
+    try:
+        idx.search(np.zeros((1, idx.dim), np.float32), 1)
+        raise AssertionError("a search before the connection must fail")
+    except ValueError as e:
+        assert "octexB200CommInit" in str(e), e
     odist.connect(idx)
     idx.set_projection(ordered=True)  # coordinates the CPU checker reproduces bit for bit
     queries = np.load(os.path.join(path, "queries.npy"))
@@ -39,8 +46,14 @@ def worker(rank, world, port, path, out, placement):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("placement", ["shard", "replicate"])
-def test_two_processes(wide_index, oracle, tmp_path, placement):
+@pytest.mark.parametrize("placement,tiers", [
+    ("shard", {}),                                                # table dealt by rows (always, as the reference)
+    ("replicate", {}),
+    ("shard", dict(shard_vectors=True, sketch="shard")),          # every row array dealt over the two GPUs
+    ("replicate", dict(shard_vectors=True, sketch="shard")),
+    ("shard", dict(vectors_on_host=True, table_on_host=True)),    # host tiers with dealt copies
+])
+def test_two_processes(wide_index, oracle, tmp_path, placement, tiers):
     import torch
     import torch.multiprocessing as mp
     from octex_b200 import index_dir
@@ -52,7 +65,7 @@ def test_two_processes(wide_index, oracle, tmp_path, placement):
     index_dir.write_index(path, arrays, meta)
     np.save(os.path.join(path, "queries.npy"), queries)
     port = 29900 + os.getpid() % 90
-    mp.spawn(worker, args=(2, port, path, str(tmp_path), placement), nprocs=2, join=True)
+    mp.spawn(worker, args=(2, port, path, str(tmp_path), placement, tiers), nprocs=2, join=True)
     ox = oracle.Index(arrays, meta)
     parts = 2 if placement == "shard" else 1
     want = {

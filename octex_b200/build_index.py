@@ -272,7 +272,8 @@ def build_arrays(dataset, params: IndexParams, device: str | torch.device = "cpu
     prev_tf32 = torch.backends.cuda.matmul.allow_tf32
     torch.backends.cuda.matmul.allow_tf32 = False
     try:
-        x16 = torch.as_tensor(np.asarray(dataset)).to(dev).to(torch.float16)
+        src = dataset.detach() if torch.is_tensor(dataset) else torch.as_tensor(np.asarray(dataset))
+        x16 = src.to(dev).to(torch.float16)
         n, dim = x16.shape
         if dim % 2:
             raise ValueError("octex: the dimension must be even")

@@ -11,6 +11,8 @@ from __future__ import annotations
 import ctypes as C
 import json
 import os
+import shutil
+import tempfile
 
 import numpy as np
 
@@ -22,6 +24,14 @@ SEARCH_PARAMS = ("read", "starts", "waves", "rerank", "wave_rerank", "batch", "s
 _SWITCHES = ("use_graph",)  # fields of the C struct the reference's Python layer does not expose
 LOAD_PARAMS = ("devices", "placement", "vectors_on_host", "shard_vectors", "table_on_host",
                "sketch", "parts", "copies_per_part", "copies_limit", "list_limit")
+# fields of cuvs::neighbors::octex::index_params (cpp/include/cuvs/neighbors/octex.hpp:32-92); the
+# builder of this package (tooling, octex_b200/build_index.py) uses the first group and accepts the
+# second without effect (they choose between build strategies of the reference's builder)
+INDEX_PARAMS = ("copies", "blocks", "pca_dims", "spacings", "list_len", "min_cell", "log_buckets",
+                "sketch_width", "table_len", "reverse_edges", "seed", "devices",
+                "exact_lists", "list_probes", "member_lists", "exact_table_max", "table_passes",
+                "table_sketch_order", "write_behind")
+_BUILDER_FIELDS = INDEX_PARAMS[:11]
 PLACEMENTS = ("shard", "replicate")
 SKETCH_PLACEMENTS = ("replicate", "shard", "host")
 
@@ -44,6 +54,35 @@ def _torch():
 def _is_torch(a):
     t = _torch()
     return t is not None and isinstance(a, t.Tensor)
+
+
+def adopt(a):
+    """``(array, back)``: numpy arrays and torch tensors pass through with ``back`` None. An array
+    of another framework (CuPy, anything with ``__dlpack__`` or ``__cuda_array_interface__``)
+    becomes a torch view of the same memory, and ``back`` turns a torch result into that
+    framework's array when its module offers ``from_dlpack`` (else the torch tensor is returned) —
+    results come back in the framework of the queries (octex/_arrays.py:32-150 of the reference)."""
+    if isinstance(a, np.ndarray) or _is_torch(a):
+        return a, None
+    torch = _torch()
+    if torch is not None and hasattr(a, "__dlpack__"):
+        t = torch.from_dlpack(a)
+    elif torch is not None and hasattr(a, "__cuda_array_interface__"):
+        t = torch.as_tensor(a, device="cuda")
+    else:
+        return np.asarray(a), None
+    import sys
+    home = sys.modules.get(type(a).__module__.split(".")[0])
+    give = getattr(home, "from_dlpack", None)
+    return t, (lambda r: give(r) if give is not None else r)
+
+
+def stored_vectors(path):
+    """The fp16 vectors of an index directory, memory-mapped [n, dim]."""
+    with open(os.path.join(os.fspath(path), "meta.json")) as f:
+        meta = json.load(f)
+    name = meta.get("files", {}).get("vectors", "vectors.npy")
+    return np.load(name if os.path.isabs(name) else os.path.join(os.fspath(path), name), mmap_mode="r")
 
 
 class _Resources:
@@ -167,6 +206,18 @@ class Index:
             _lib.lib().cuvsOctexIndexDestroy(self._h)
             self._h = None
 
+    def save(self, path):
+        """Copy the index directory to ``path`` (a new or empty directory); ``load(path)`` restores
+        the index (octex/index.py:259-270 of the reference)."""
+        path = os.fspath(path)
+        if self._path is None:
+            raise ValueError("octex: this index was attached from arrays in memory and has no directory")
+        if os.path.exists(path) and (not os.path.isdir(path) or os.listdir(path)):
+            raise FileExistsError(f"octex: {path} exists and is not an empty directory")
+        if os.path.abspath(path) != os.path.abspath(self._path):
+            shutil.copytree(self._path, path, dirs_exist_ok=True)
+        return path
+
     def __del__(self):
         try:
             self.close()
@@ -186,6 +237,14 @@ class Index:
         k = int(k)
         if k <= 0:
             raise ValueError("octex: k must be positive")
+        queries, back = adopt(queries)
+        if back is not None:  # another framework's arrays: work on torch views, hand back its own kind
+            neighbors = None if neighbors is None else adopt(neighbors)[0]
+            distances = None if distances is None else adopt(distances)[0]
+            D, I = self.search(queries, k, read=read, starts=starts, waves=waves, rerank=rerank,
+                               wave_rerank=wave_rerank, batch=batch, sketch_rank=sketch_rank,
+                               final_rerank=final_rerank, neighbors=neighbors, distances=distances)
+            return back(D), back(I)
         p = search_params(read=read, starts=starts, waves=waves, rerank=rerank,
                           wave_rerank=wave_rerank, batch=batch, sketch_rank=sketch_rank,
                           final_rerank=final_rerank)
@@ -313,6 +372,47 @@ def load(path, devices=None, placement="shard", vectors_on_host=False, *, shard_
         raise
     del keep
     return Index(h, path)
+
+
+def build(dataset, path=None, *, metric="sqeuclidean", placement="shard", vectors_on_host=False,
+          table_on_host=False, shard_vectors=False, sketch="replicate", **index_params):
+    """Build an index of ``dataset`` [n, dim] (float32 or float16; numpy, torch, or any array
+    ``adopt`` understands) and load it — the call of the reference's ``octex.build``
+    (octex/index.py:337-375).  The directory goes to ``path``, or to a temporary directory that
+    lives as long as the returned index (``Index.save`` keeps it).  Keyword arguments are the
+    fields of ``index_params``; ``devices`` selects the GPU the index is loaded on.
+
+    The builder behind this call is this package's tooling (``octex_b200.build_index``: exact member
+    lists and an exact neighbor table, on the GPU when there is one), meant for data of up to a few
+    million rows; it writes the reference's directory format."""
+    from . import build_index
+    check_metric(metric)
+    unknown = set(index_params) - set(INDEX_PARAMS)
+    if unknown:
+        raise TypeError(f"octex: unknown index parameters {sorted(unknown)}")
+    torch = _torch()
+    data, _ = adopt(dataset)
+    dt = str(data.dtype).replace("torch.", "")
+    if dt not in ("float32", "float16"):
+        raise TypeError("octex: dataset must be float32 or float16")
+    if len(data.shape) != 2:
+        raise ValueError("octex: dataset must be a matrix [n, dim]")
+    fields = {k: v for k, v in index_params.items() if k in _BUILDER_FIELDS}
+    if "spacings" in fields:
+        fields["spacings"] = [float(f) for f in fields["spacings"]]
+    tmp = None
+    if path is None:
+        tmp = tempfile.TemporaryDirectory(prefix="octex-")
+        path = tmp.name
+    path = os.fspath(path)
+    os.makedirs(path, exist_ok=True)
+    device = "cuda" if torch is not None and torch.cuda.is_available() else "cpu"
+    build_index.build(data, path, build_index.IndexParams(**fields), device=device)
+    idx = load(path, devices=index_params.get("devices"), placement=placement,
+               vectors_on_host=vectors_on_host, table_on_host=table_on_host,
+               shard_vectors=shard_vectors, sketch=sketch)
+    idx._tmpdir = tmp
+    return idx
 
 
 def _address(a):

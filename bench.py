@@ -75,12 +75,15 @@ class ClockSampler:
 
     def __init__(self, gpu):
         self.gpu, self.rows, self.proc = gpu, [], None
+        self.t0 = self.t1 = None
 
     def __enter__(self):
+        """Starts sampling (before the warm-up, so that samples are already arriving when the timed
+        region begins); ``begin`` / ``end`` bracket the timed region."""
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.gpu), f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -88,22 +91,32 @@ class ClockSampler:
             self.proc = None
         return self
 
+    def begin(self):
+        self.t0 = time.perf_counter()
+
+    def end(self):
+        self.t1 = time.perf_counter()
+
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append((time.perf_counter(), [c.strip() for c in line.split(",")]))
 
     def __exit__(self, *exc):
         if self.proc is not None:
-            time.sleep(0.15)
+            time.sleep(0.05)
             self.proc.terminate()
             self.proc.wait(timeout=5)
 
     def summary(self):
-        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
-        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+        rows = [r for t, r in self.rows
+                if self.t0 is not None and self.t0 <= t <= (self.t1 or t) + 0.03]
+        if not rows:  # a region shorter than the sampling period: the samples nearest to it
+            rows = [r for _, r in self.rows[-3:]]
+        sm = [float(r[0]) for r in rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
         reasons = [n for i, n in enumerate(names)
-                   if any(len(r) >= 6 and r[2 + i].lower().startswith("active") for r in self.rows)]
+                   if any(len(r) >= 6 and r[2 + i].lower().startswith("active") for r in rows)]
         return {"sm_mhz": statistics.median(sm) if sm else None,
                 "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
                 "samples": len(sm)}
@@ -267,12 +280,14 @@ def main():
 
     # ---- value: queries resident on the GPU, one graph replay per step ----
     idx.search(q_dev, K, **sp)  # leaves the batch on the GPU
-    for _ in range(args.warmup):
-        idx.search_resident(nq, K, stream=stream.cuda_stream, **sp)
-    barrier()
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
           for _ in range(args.steps)]
     with ClockSampler(local) as clocks:
+        for _ in range(args.warmup):
+            flush.fill_(1)
+            idx.search_resident(nq, K, stream=stream.cuda_stream, **sp)
+        barrier()
+        clocks.begin()
         wall0 = time.perf_counter()
         for a, b in ev:
             flush.fill_(1)  # evict the index from L2 between timed steps
@@ -281,6 +296,7 @@ def main():
             b.record(stream)
         torch.cuda.synchronize()
         wall = time.perf_counter() - wall0
+        clocks.end()
     step_ms = [a.elapsed_time(b) for a, b in ev]
     total_ms = sum(step_ms)
     barrier()

@@ -313,11 +313,14 @@ __device__ __forceinline__ void sketch_rows(const int* cand, int n, const signed
 /// Rows j and j + stride of a lane group: squared distances of two fp16 rows to the query fq
 /// (shared memory, read 16 bytes at a time).
 /// Both row pointers are valid (a row that is not wanted is replaced by any row by the caller, who
-/// drops the result). kWhole: D is a multiple of 128, so no step needs a bounds check.
-template <bool kWhole>
-__device__ __forceinline__ void exact_pair(const uint4* const (&row)[2], int D, int sub, const float* fq,
+/// drops the result). kMode 0: any D that is a multiple of 8; 1: D a multiple of 128, so no step
+/// needs a bounds check; 2: D = 128, one step with constant offsets.
+template <int kMode>
+__device__ __forceinline__ void exact_pair(const uint4* const (&row)[2], int Drt, int sub, const float* fq,
                                            float (&out)[2])
 {
+  constexpr bool kWhole = kMode != 0;
+  const int D           = kMode == 2 ? 128 : Drt;
   float acc[2][4];
 #pragma unroll
   for (int u = 0; u < 2; u++)
@@ -370,35 +373,45 @@ __device__ __forceinline__ void exact_pair(const uint4* const (&row)[2], int D, 
 /// 1, 2, 4, 8, 16 (search_kernels.cuh:325-342 is the reference's warp-per-row form of the same
 /// sum). Eight lanes own a row, each reading 16 bytes per step (partial sums 4 lane .. 4 lane + 3);
 /// a warp works on eight rows at a time.
+template <bool kDealt, int kMode>
+__device__ __forceinline__ void exact_rows(const int* sid, int ns, const __half* __restrict__ vectors,
+                                           const row_map& map, int Drt, const float* fq, float* sdv)
+{
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int sub = lane & 7, grp = lane >> 3;
+  const int D   = kMode == 2 ? 128 : Drt;
+  for (int jb = warp * 4 + grp; jb < ns + warp * 4 + grp; jb += nw * 8) {
+    int j[2];
+    bool wanted[2];
+    const uint4* row[2];
+#pragma unroll
+    for (int u = 0; u < 2; u++) {
+      j[u]         = jb + u * nw * 4;
+      const int id = j[u] < ns ? sid[j[u]] : -1;
+      wanted[u]    = id >= 0;
+      // a slot without a row works on a row this GPU holds (cached after its first use) and drops
+      // the result
+      row[u] = reinterpret_cast<const uint4*>(row_of<kDealt>(vectors, map, wanted[u] ? id : map.local, D));
+    }
+    float out[2];
+    exact_pair<kMode>(row, D, sub, fq, out);
+#pragma unroll
+    for (int u = 0; u < 2; u++)
+      if (wanted[u] && sub == 0) sdv[j[u]] = out[u];
+  }
+}
+
 template <bool kDealt>
 __device__ __forceinline__ void exact_distances(const int* sid, int ns, const __half* __restrict__ vectors,
                                                 const row_map& map, int D, const float* fq, float* sdv)
 {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  if ((D & 7) == 0) {
-    const int sub = lane & 7, grp = lane >> 3;
-    for (int jb = 0; jb < ns; jb += nw * 8) {
-      int j[2];
-      bool wanted[2];
-      const uint4* row[2];
-#pragma unroll
-      for (int u = 0; u < 2; u++) {
-        j[u]         = jb + u * nw * 4 + warp * 4 + grp;
-        const int id = j[u] < ns ? sid[j[u]] : -1;
-        wanted[u]    = id >= 0;
-        // a slot without a row works on a row this GPU holds (cached after its first use) and drops
-        // the result
-        row[u] = reinterpret_cast<const uint4*>(row_of<kDealt>(vectors, map, wanted[u] ? id : map.local, D));
-      }
-      float out[2];
-      if ((D & 127) == 0)
-        exact_pair<true>(row, D, sub, fq, out);
-      else
-        exact_pair<false>(row, D, sub, fq, out);
-#pragma unroll
-      for (int u = 0; u < 2; u++)
-        if (wanted[u] && sub == 0) sdv[j[u]] = out[u];
-    }
+  if (D == 128) {
+    exact_rows<kDealt, 2>(sid, ns, vectors, map, D, fq, sdv);
+  } else if ((D & 127) == 0) {
+    exact_rows<kDealt, 1>(sid, ns, vectors, map, D, fq, sdv);
+  } else if ((D & 7) == 0) {
+    exact_rows<kDealt, 0>(sid, ns, vectors, map, D, fq, sdv);
   } else {
     for (int j = warp; j < ns; j += nw) {
       if (sid[j] < 0) continue;

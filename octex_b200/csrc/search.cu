@@ -427,9 +427,8 @@ auto make_plan(index_impl& ix, search_params const& sp, int m, int k, debug_opti
   OCTEX_CUDA_TRY(cudaStreamSynchronize(p.stream));
   check_tc(pl);
   OCTEX_CUDA_TRY(cudaEventCreateWithFlags(&pl.done_ev, cudaEventDisableTiming));
-  // batches that exchange data between processes are launched kernel by kernel (the NCCL calls
-  // sit between the kernels); a single process replays one graph per batch
-  if (ix.world > 1) return plp;
+  // one graph per batch; with several processes the NCCL exchanges between the kernels are captured
+  // into it too (every process replays its graph in the same order, as it would launch the calls)
   cudaGraph_t graph = nullptr;
   OCTEX_CUDA_TRY(cudaStreamBeginCapture(p.stream, cudaStreamCaptureModeThreadLocal));
   try {

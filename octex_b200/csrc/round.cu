@@ -272,14 +272,16 @@ __device__ __forceinline__ bool may_prefetch(const row_map& m)
 /// lanes (strides 1, 2, 4, ...); a lane group has four rows in flight. Straight-line code: a lane
 /// past the last row or past the last chunk works on a valid stand-in and its result is dropped
 /// (a chunk past the end has scale and query 0, so it adds exactly 0).
-template <int kLw, bool kDealt>
+/// kFull: the sketch is exactly 8 * kLw codes wide (a power of two), a compile-time width.
+template <int kLw, bool kDealt, bool kFull = false>
 __device__ __forceinline__ void sketch_rows(const int* cand, int n, const signed char* __restrict__ sketch,
-                                            const row_map& map, int S, const float* sc, const float* qv,
+                                            const row_map& map, int Srt, const float* sc, const float* qv,
                                             float* dist)
 {
   constexpr int kG = 32 / kLw;  // rows per warp and step
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   const int sub = lane % kLw, grp = lane / kLw;
+  const int S      = kFull ? 8 * kLw : Srt;
   const int chunks = S / 8;
   const bool live  = sub < chunks;
   const int subc   = live ? sub : 0;
@@ -743,7 +745,11 @@ __global__ void __launch_bounds__(kRoundThreads, 8) round_kernel(const round_arg
   // query coordinates in registers, the chunks of a row summed by a butterfly over its lanes
   // (strides 1, 2, 4, ...); four rows per lane group in flight. A sketch wider than 256 gives a
   // lane a second chunk (c + 32), added last.
-  if (S <= 8) {
+  if (S == 64) {
+    sketch_rows<8, kDealt, true>(cand, n, a.sketch, a.sketch_map, S, sc, qv, dist);
+  } else if (S == 128) {
+    sketch_rows<16, kDealt, true>(cand, n, a.sketch, a.sketch_map, S, sc, qv, dist);
+  } else if (S <= 8) {
     sketch_rows<1, kDealt>(cand, n, a.sketch, a.sketch_map, S, sc, qv, dist);
   } else if (S <= 16) {
     sketch_rows<2, kDealt>(cand, n, a.sketch, a.sketch_map, S, sc, qv, dist);

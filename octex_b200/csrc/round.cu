@@ -169,19 +169,31 @@ struct radix_cut_t {
 
 /// Threshold of the R smallest of n distinct 64-bit keys (n > R): 8-bit radix passes from the top
 /// bits, stopping at the first pass whose bucket is taken whole. On return exactly R keys k satisfy
-/// (k & mask) <= prefix. key_at(i) gives key i. All threads of the block call it.
-template <typename KeyAt>
-__device__ __forceinline__ radix_cut_t radix_cut(KeyAt key_at, int n, int R, unsigned* hist, int* ctrl)
+/// (k & mask) <= prefix. hi_at(i) / lo_at(i) give the two 32-bit words of key i; the passes over
+/// the high word (the distance) never touch the low one (the id), which only breaks ties. All
+/// threads of the block call it.
+template <typename HiAt, typename LoAt>
+__device__ __forceinline__ radix_cut_t radix_cut(HiAt hi_at, LoAt lo_at, int n, int R, unsigned* hist,
+                                                 int* ctrl)
 {
-  radix_cut_t c{0ULL, 0ULL};
+  unsigned prefix_hi = 0u, mask_hi = 0u, prefix_lo = 0u, mask_lo = 0u;
   int need = R;
-  for (int shift = 56; shift >= 0; shift -= 8) {
+  for (int pass = 0; pass < 8; pass++) {
+    const int word = pass < 4 ? 1 : 0, shift = 24 - 8 * (pass & 3);
     for (int i = threadIdx.x; i < 256; i += blockDim.x)
       hist[i] = 0;
     __syncthreads();
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
-      const unsigned long long k = key_at(i);
-      if ((k & c.mask) == c.prefix) atomicAdd(&hist[(k >> shift) & 255], 1u);
+    if (word == 1) {
+      for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const unsigned h = hi_at(i);
+        if ((h & mask_hi) == prefix_hi) atomicAdd(&hist[(h >> shift) & 255], 1u);
+      }
+    } else {
+      for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        if (hi_at(i) != prefix_hi) continue;
+        const unsigned l = lo_at(i);
+        if ((l & mask_lo) == prefix_lo) atomicAdd(&hist[(l >> shift) & 255], 1u);
+      }
     }
     __syncthreads();
     if (threadIdx.x < 32) {
@@ -218,13 +230,19 @@ __device__ __forceinline__ radix_cut_t radix_cut(KeyAt key_at, int n, int R, uns
     }
     __syncthreads();
     const int digit = ctrl[1], left = ctrl[2], bucket = ctrl[3];
-    c.prefix |= static_cast<unsigned long long>(digit) << shift;
-    c.mask |= 255ULL << shift;
+    if (word == 1) {
+      prefix_hi |= static_cast<unsigned>(digit) << shift;
+      mask_hi |= 255u << shift;
+    } else {
+      prefix_lo |= static_cast<unsigned>(digit) << shift;
+      mask_lo |= 255u << shift;
+    }
     need = left;
     __syncthreads();
     if (bucket == left) break;
   }
-  return c;
+  return radix_cut_t{(static_cast<unsigned long long>(prefix_hi) << 32) | prefix_lo,
+                     (static_cast<unsigned long long>(mask_hi) << 32) | mask_lo};
 }
 
 /// Eight int8 codes (two 32-bit words) against eight (scale, query) pairs: sum of
@@ -491,8 +509,9 @@ __device__ __forceinline__ void merge_into_kept(unsigned long long* pool,
     for (int i = threadIdx.x; i < max(width, 64); i += blockDim.x)
       sorted[i] = i < total ? pool[i] : kNoKey;
   } else {
-    auto key_at         = [&](int i) { return pool[i]; };
-    const radix_cut_t c = radix_cut(key_at, total, KO, hist, ctrl);
+    auto hi_at          = [&](int i) { return static_cast<unsigned>(pool[i] >> 32); };
+    auto lo_at          = [&](int i) { return static_cast<unsigned>(pool[i]); };
+    const radix_cut_t c = radix_cut(hi_at, lo_at, total, KO, hist, ctrl);
     if (threadIdx.x == 0) ctrl[0] = 0;
     __syncthreads();
     for (int i = threadIdx.x; i < total; i += blockDim.x) {
@@ -822,7 +841,9 @@ __global__ void __launch_bounds__(kRoundThreads, 8) round_kernel(const round_arg
   int ns      = n;
   if (n > R) {
     auto key_at = [&](int i) { return rank_key(dist[i], static_cast<unsigned>(cand[i])); };
-    const radix_cut_t c = radix_cut(key_at, n, R, hist, ctrl);
+    auto hi_at          = [&](int i) { return __float_as_uint(dist[i]); };
+    auto lo_at          = [&](int i) { return static_cast<unsigned>(cand[i]); };
+    const radix_cut_t c = radix_cut(hi_at, lo_at, n, R, hist, ctrl);
     if (threadIdx.x == 0) ctrl[0] = 0;
     __syncthreads();
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
@@ -883,12 +904,12 @@ __global__ void __launch_bounds__(kRoundThreads, 8) round_kernel(const round_arg
   if (!a.sketch_rank) {
     // every row about to be read is asked for at once (128-byte lines into L2), so the distance
     // loop below finds most of them on the way
-    const int lines = (a.D * 2 + 127) >> 7;
-    for (int i = threadIdx.x; i < (may_prefetch<kDealt>(a.vector_map) ? ns * lines : 0); i += blockDim.x) {
-      const int r = i / lines;
+    const int row_bytes = a.D * 2;
+    for (int r = threadIdx.x; r < (may_prefetch<kDealt>(a.vector_map) ? ns : 0); r += blockDim.x) {
       if (sid[r] < 0) continue;
-      asm volatile("prefetch.global.L2 [%0];" ::"l"(
-        reinterpret_cast<const char*>(a.vectors + static_cast<int64_t>(sid[r]) * a.D) + 128 * (i - r * lines)));
+      const char* row = reinterpret_cast<const char*>(a.vectors + static_cast<int64_t>(sid[r]) * a.D);
+      for (int b = 0; b < row_bytes; b += 128)
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(row + b));
     }
     if (a.stats != nullptr) {
       int mine = 0;

@@ -24,6 +24,14 @@ def copies_of(copies: int, rank: int, world: int):
     return copies * rank // world, copies * (rank + 1) // world
 
 
+def rows_of(n: int, rank: int, world: int):
+    """Rows [r0, r1) of an array dealt by rows that process ``rank`` holds: ranges of
+    ``ceil(n / world)`` rows (load.cu:315,406-427).  The owner of row ``i`` is ``i // rows_per``."""
+    rows_per = (n + world - 1) // world
+    r0 = min(n, rank * rows_per)
+    return r0, min(n, r0 + rows_per)
+
+
 def connect(index, group=None):
     """Create the NCCL communicator of ``index`` among the processes of ``group`` (default: all of
     torch.distributed).  Collective: every process calls it."""

@@ -87,3 +87,36 @@ def test_two_rank_shard_rules(small_index, oracle, tmp_path):
         lo, hi = int(got["lo"]), int(got["hi"])
         assert np.array_equal(got["ids"], t["kept1_ids"][lo:hi])
         assert np.array_equal(got["dist"].view(np.uint32), t["kept1_dist"][lo:hi].view(np.uint32))
+
+
+def rows_worker(rank, world, port, out):
+    """Every rank keeps its range of a row array; a row is fetched from the rank that owns it."""
+    sys.path.insert(0, ROOT)
+    from octex_b200 import dist as odist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    n, width = 1003, 6
+    full = np.arange(n * width, dtype=np.int64).reshape(n, width)  # what a whole array would hold
+    r0, r1 = odist.rows_of(n, rank, world)
+    rows_per = (n + world - 1) // world
+    mine = torch.as_tensor(full[r0:r1].copy())
+    pad = torch.zeros((rows_per, width), dtype=torch.int64)
+    pad[: r1 - r0] = mine
+    everyone = [torch.zeros_like(pad) for _ in range(world)]
+    dist.all_gather(everyone, pad)  # stands for mapping the other ranks' ranges
+    rng = np.random.default_rng(rank)
+    ids = rng.integers(0, n, size=200)
+    got = np.stack([everyone[i // rows_per][i - (i // rows_per) * rows_per].numpy() for i in ids])
+    assert np.array_equal(got, full[ids])
+    np.save(os.path.join(out, f"rows{rank}.npy"), np.array([r0, r1]))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_rows_dealt_over_ranks(tmp_path, world):
+    port = 29700 + os.getpid() % 90 + world
+    mp.spawn(rows_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    spans = [np.load(tmp_path / f"rows{r}.npy") for r in range(world)]
+    assert spans[0][0] == 0 and spans[-1][1] == 1003
+    assert all(spans[r][1] == spans[r + 1][0] for r in range(world - 1))

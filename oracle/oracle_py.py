@@ -48,6 +48,15 @@ def build(force: bool = False) -> str:
     so = os.path.join(_HERE, "liboctex_oracle.so")
     src = [os.path.join(_HERE, f) for f in ("octex_oracle.cpp", "octex_oracle.h", "e8_port.hpp")]
     stale = not os.path.exists(so) or any(os.path.getmtime(s) > os.path.getmtime(so) for s in src)
+    # where the reference sources are mounted, its own code compiled into _ref/ must be there too
+    reference = os.environ.get("REFERENCE", "/root/reference")
+    if os.path.exists(os.path.join(reference, "cpp/src/neighbors/octex/detail/search_kernels.cuh")):
+        outs = ("libe8_ref.so", "libe8_ref_fma.so", "libe8_ref_cuda.so", "libref_search.so")
+        shims = [os.path.join(_HERE, f) for f in ("ref_e8_shim.cpp", "ref_e8_cuda_shim.cu", "ref_search_shim.cu")]
+        for name in outs:
+            p = os.path.join(_HERE, "_ref", name)
+            if not os.path.exists(p) or any(os.path.getmtime(s) > os.path.getmtime(p) for s in shims):
+                stale = True
     if force or stale:
         subprocess.check_call(["make", "-C", _HERE, "all"], stdout=subprocess.DEVNULL)
     return so
@@ -189,3 +198,71 @@ def brute_force(base, queries, k=10, threads=0):
     if rc != 0:
         raise RuntimeError(lib().oracle_last_error().decode())
     return ids, d
+
+
+# ---- the reference's own search kernels on the GPU (oracle/_ref/libref_search.so) ----------------
+
+class _RefSearchArgs(C.Structure):
+    _fields_ = [("n", C.c_int64),
+                ("dim", C.c_int32), ("copies", C.c_int32), ("blocks", C.c_int32), ("levels", C.c_int32),
+                ("list_len", C.c_int32), ("log_buckets", C.c_int32), ("sketch_width", C.c_int32),
+                ("table_len", C.c_int32),
+                ("stride", C.c_int64), ("mmax", C.c_int64),
+                ("inv_f", C.c_void_p), ("lists", C.c_void_p), ("keys", C.c_void_p),
+                ("offsets", C.c_void_p), ("base", C.c_void_p), ("scale", C.c_void_p),
+                ("sketch", C.c_void_p), ("vectors", C.c_void_p), ("table", C.c_void_p),
+                ("m", C.c_int32), ("y", C.c_void_p), ("qs", C.c_void_p), ("q", C.c_void_p),
+                ("read", C.c_int32), ("starts", C.c_int32), ("waves", C.c_int32),
+                ("rerank", C.c_int32), ("wave_rerank", C.c_int32), ("k", C.c_int32),
+                ("seg", C.c_void_p), ("w1", C.c_int32), ("cand1", C.c_void_p), ("dist1", C.c_void_p),
+                ("n1", C.c_void_p), ("kept1_ids", C.c_void_p), ("kept1_dist", C.c_void_p),
+                ("kept_ids", C.c_void_p), ("kept_dist", C.c_void_p)]
+
+
+def ref_search():
+    """The reference's search kernels compiled as device code (needs a GPU), or None when not built."""
+    p = os.path.join(_HERE, "_ref", "libref_search.so")
+    return C.CDLL(p) if os.path.exists(p) else None
+
+
+def ref_search_pipeline(arrays, meta, y, qs, queries, k=10, *, read=32, starts=128, waves=2,
+                        rerank=128, wave_rerank=128):
+    """Run the reference's probe / gather / rerank / pick-starts kernels on this machine's GPU on a
+    batch whose projected coordinates ``y`` (fp16 bits), sketch-space queries ``qs`` and queries are
+    given.  Returns a dict: seg, cand1, dist1, n1, kept1_ids, kept1_dist, kept_ids, kept_dist."""
+    lib_ = ref_search()
+    keep = {name: np.ascontiguousarray(arrays[name]) for name in
+            ("lists", "keys", "offsets", "base", "sketch_scale", "sketch", "vectors", "table")}
+    keep["vectors"] = keep["vectors"].view(np.uint16)
+    inv_f = np.asarray([np.float32(1.0 / float(f)) for f in meta["spacings"]], np.float32)
+    y = np.ascontiguousarray(y, np.uint16)
+    qs = np.ascontiguousarray(qs, np.float32)
+    q = np.ascontiguousarray(queries, np.float32)
+    m, C_ = len(q), meta["copies"]
+    KO = max(starts, k)
+    w1 = 1
+    while w1 < 1.5 * C_ * min(read, meta["list_len"]) or w1 < 2048:
+        w1 <<= 1
+    out = dict(seg=np.zeros((m, C_, 2), np.int32), cand1=np.zeros((m, w1), np.int32),
+               dist1=np.zeros((m, w1), np.float32), n1=np.zeros(m, np.int32),
+               kept1_ids=np.zeros((m, KO), np.int64), kept1_dist=np.zeros((m, KO), np.float32),
+               kept_ids=np.zeros((m, KO), np.int64), kept_dist=np.zeros((m, KO), np.float32))
+    a = _RefSearchArgs()
+    a.n, a.dim, a.copies, a.blocks = meta["n"], meta["dim"], C_, meta["blocks"]
+    a.levels, a.list_len, a.log_buckets = len(meta["spacings"]), meta["list_len"], meta["log_buckets"]
+    a.sketch_width, a.table_len = meta["sketch_width"], meta["table_len"]
+    a.stride, a.mmax = keep["lists"].shape[1], keep["keys"].shape[2]
+    a.inv_f = inv_f.ctypes.data
+    for field, name in (("lists", "lists"), ("keys", "keys"), ("offsets", "offsets"), ("base", "base"),
+                        ("scale", "sketch_scale"), ("sketch", "sketch"), ("vectors", "vectors"),
+                        ("table", "table")):
+        setattr(a, field, keep[name].ctypes.data)
+    a.m, a.y, a.qs, a.q = m, y.ctypes.data, qs.ctypes.data, q.ctypes.data
+    a.read, a.starts, a.waves, a.rerank, a.wave_rerank, a.k = read, starts, waves, rerank, wave_rerank, k
+    a.w1 = w1
+    for name, arr in out.items():
+        setattr(a, name, arr.ctypes.data)
+    rc = lib_.ref_search_pipeline(C.byref(a))
+    if rc != 0:
+        raise RuntimeError(f"the reference kernels returned {rc}")
+    return out

@@ -1,0 +1,187 @@
+// TEST INFRASTRUCTURE ONLY. The reference's own search kernels
+// (cpp/src/neighbors/octex/detail/search_kernels.cuh of hpdic/octex: probe_kernel, gather_kernel,
+// rerank_keep_kernel, pick_starts_kernel) compiled unmodified as device code and launched with the
+// launch shapes of the reference's search.cu (:344-357, :393, :433-450, :453, :488), behind one
+// host function with host pointers in and out. A GPU test feeds it the projected coordinates,
+// sketch-space queries and queries of a batch and compares what the reference's kernels make of
+// them — segments, candidate sets, sketch distances, kept lists — with the CPU checker, which is
+// what pins the checker to the reference beyond the E8 decode. The header is included from where
+// the reference sources lie; nothing of it is copied here. The only stand-in is a one-line
+// raft/core/detail/macros.hpp (shim/) that defines RAFT_KERNEL.
+#include "search_kernels.cuh"
+
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstdint>
+#include <vector>
+
+namespace ref = cuvs::neighbors::octex::detail;
+
+namespace {
+
+struct device_array {
+  void* p = nullptr;
+  cudaError_t err = cudaSuccess;
+  device_array(const void* host, size_t bytes, bool copy = true)
+  {
+    err = cudaMalloc(&p, std::max<size_t>(bytes, 16));
+    if (err == cudaSuccess && host != nullptr && copy && bytes != 0)
+      err = cudaMemcpy(p, host, bytes, cudaMemcpyHostToDevice);
+  }
+  device_array(device_array const&) = delete;
+  ~device_array() { cudaFree(p); }
+  template <typename T>
+  T* as() const
+  {
+    return static_cast<T*>(p);
+  }
+};
+
+int log2_ceil(int64_t v)
+{
+  int e = 0;
+  while ((int64_t{1} << e) < v)
+    e++;
+  return e;
+}
+
+int hash_log_for(int64_t entries)
+{
+  const int e = log2_ceil(static_cast<int64_t>(std::ceil(entries * ref::kHashGrow)));
+  return std::clamp(e, ref::kMinLogHash, log2_ceil(ref::kMaxHash));
+}
+
+size_t gather_smem(int W, int sw, int C) { return static_cast<size_t>(W + 2 * sw + 2 * C + 1) * sizeof(int); }
+
+}  // namespace
+
+struct ref_search_args {
+  // index (arrays of an index directory, host memory)
+  int64_t n;
+  int32_t dim, copies, blocks, levels, list_len, log_buckets, sketch_width, table_len;
+  int64_t stride, mmax;
+  const float* inv_f;         // [levels]
+  const int32_t* lists;       // [copies, stride]
+  const int64_t* keys;        // [copies, levels, mmax]
+  const int32_t* offsets;     // [copies, levels, 2^log_buckets + 1]
+  const int32_t* base;        // [copies, levels]
+  const float* scale;         // [sketch_width]
+  const int8_t* sketch;       // [n, sketch_width]
+  const uint16_t* vectors;    // fp16 [n, dim]
+  const int32_t* table;       // [n, table_len]
+  // batch
+  int32_t m;
+  const uint16_t* y;          // fp16 [m, copies * 8 * blocks] projected coordinates
+  const float* qs;            // [m, sketch_width]
+  const float* q;             // [m, dim] uncentred queries
+  // parameters
+  int32_t read, starts, waves, rerank, wave_rerank, k;
+  // results
+  int32_t* seg;               // [m, copies, 2]
+  int32_t w1;                 // capacity of cand1 / dist1 per query (>= the hash set of round 1)
+  int32_t* cand1;             // [m, w1]
+  float* dist1;               // [m, w1]
+  int32_t* n1;                // [m]
+  int64_t* kept1_ids;         // [m, KO] after the first round
+  float* kept1_dist;
+  int64_t* kept_ids;          // [m, KO] after the waves
+  float* kept_dist;
+};
+
+// Returns 0, a CUDA error code, or -1 for arguments the kernels cannot take.
+extern "C" int ref_search_pipeline(const ref_search_args* a)
+{
+  const int m = a->m, C = a->copies, L = a->levels, S = a->sketch_width, D = a->dim;
+  const int lr = std::min(a->read, a->list_len);
+  const int KO = std::max(a->starts, a->k);
+  const int64_t T1 = (int64_t{1} << a->log_buckets) + 1;
+  if (a->blocks != 2 && a->blocks != 4) return -1;
+  if (a->rerank > ref::kMaxRerank || a->wave_rerank > ref::kMaxRerank) return -1;
+  if (KO + std::max(a->rerank, a->wave_rerank) > ref::kMaxKeepSort) return -1;
+  const int logW = hash_log_for(int64_t{C} * lr), W = 1 << logW;
+  if (a->w1 < W) return -1;
+  const int logW2 = hash_log_for(int64_t{a->starts} * a->table_len), W2 = 1 << logW2;
+  const int width = 8 * a->blocks * C;
+
+  device_array inv_f(a->inv_f, sizeof(float) * L), lists(a->lists, sizeof(int32_t) * C * a->stride),
+    keys(a->keys, sizeof(int64_t) * C * L * a->mmax), offsets(a->offsets, sizeof(int32_t) * C * L * T1),
+    base(a->base, sizeof(int32_t) * C * L), scale(a->scale, sizeof(float) * S),
+    sketch(a->sketch, static_cast<size_t>(a->n) * S),
+    vectors(a->vectors, sizeof(uint16_t) * a->n * D),
+    table(a->table, sizeof(int32_t) * a->n * a->table_len), y(a->y, sizeof(uint16_t) * m * width),
+    qs(a->qs, sizeof(float) * m * S), q(a->q, sizeof(float) * m * D);
+  device_array seg(nullptr, sizeof(int2) * m * C), cand(nullptr, sizeof(int) * m * W),
+    dist(nullptr, sizeof(float) * m * W), nin(nullptr, sizeof(int) * m),
+    si(nullptr, sizeof(long long) * m * KO), sd(nullptr, sizeof(float) * m * KO),
+    seg2(nullptr, sizeof(int2) * m * std::max(a->starts, 1)),
+    cand2(nullptr, sizeof(int) * m * W2), dist2(nullptr, sizeof(float) * m * W2),
+    n2(nullptr, sizeof(int) * m),
+    done(nullptr, sizeof(long long) * m * std::max(a->starts * a->waves, 1));
+  const long long xp = reinterpret_cast<long long>(vectors.p), tp = reinterpret_cast<long long>(table.p);
+  device_array xptr(&xp, sizeof(xp)), tptr(&tp, sizeof(tp));
+  for (const device_array* d : {&inv_f, &lists, &keys, &offsets, &base, &scale, &sketch, &vectors, &table,
+                                &y, &qs, &q, &seg, &cand, &dist, &nin, &si, &sd, &seg2, &cand2, &dist2,
+                                &n2, &done, &xptr, &tptr})
+    if (d->err != cudaSuccess) return static_cast<int>(d->err);
+  cudaMemset(cand.p, 0xff, sizeof(int) * m * W);
+  cudaMemset(dist.p, 0, sizeof(float) * m * W);
+
+  // cell lookup (search.cu:105-137)
+  {
+    const int64_t tot = int64_t{m} * C;
+    const unsigned grid = static_cast<unsigned>((tot + 255) / 256);
+    if (a->blocks == 4)
+      ref::probe_kernel<4><<<grid, 256>>>(y.as<__half>(), m, C, L, inv_f.as<float>(), offsets.as<int>(), T1,
+                                          keys.as<long long>(), a->mmax, base.as<int>(), a->list_len, lr,
+                                          a->log_buckets, seg.as<int2>());
+    else
+      ref::probe_kernel<2><<<grid, 256>>>(y.as<__half>(), m, C, L, inv_f.as<float>(), offsets.as<int>(), T1,
+                                          keys.as<long long>(), a->mmax, base.as<int>(), a->list_len, lr,
+                                          a->log_buckets, seg.as<int2>());
+  }
+  // first round: gather + sketch distances (search.cu:343-361), exact rerank into the kept list (:393)
+  cudaFuncSetAttribute(ref::gather_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                       static_cast<int>(gather_smem(W, S, C)));
+  ref::gather_kernel<false><<<m, 256, gather_smem(W, S, C)>>>(
+    seg.as<int2>(), C, lists.as<int>(), a->stride, nullptr, 1, sketch.as<signed char>(), nullptr, 1,
+    scale.as<float>(), qs.as<float>(), S, W, logW, cand.as<int>(), dist.as<float>(), nin.as<int>());
+  ref::rerank_keep_kernel<<<m, 256, D * sizeof(float)>>>(cand.as<int>(), dist.as<float>(), nin.as<int>(), W,
+                                                         xptr.as<long long>(), a->n, D, q.as<float>(),
+                                                         a->rerank, KO, si.as<long long>(), sd.as<float>(),
+                                                         true);
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return static_cast<int>(e);
+  cudaMemcpy(a->seg, seg.p, sizeof(int2) * m * C, cudaMemcpyDeviceToHost);
+  cudaMemcpy2D(a->cand1, sizeof(int) * a->w1, cand.p, sizeof(int) * W, sizeof(int) * W, m, cudaMemcpyDeviceToHost);
+  cudaMemcpy2D(a->dist1, sizeof(float) * a->w1, dist.p, sizeof(float) * W, sizeof(float) * W, m,
+               cudaMemcpyDeviceToHost);
+  cudaMemcpy(a->n1, nin.p, sizeof(int) * m, cudaMemcpyDeviceToHost);
+  cudaMemcpy(a->kept1_ids, si.p, sizeof(long long) * m * KO, cudaMemcpyDeviceToHost);
+  cudaMemcpy(a->kept1_dist, sd.p, sizeof(float) * m * KO, cudaMemcpyDeviceToHost);
+
+  // waves (search.cu:432-500): start points, their table rows, rerank into the kept list
+  if (a->waves > 0) {
+    cudaFuncSetAttribute(ref::gather_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         static_cast<int>(gather_smem(W2, S, a->starts)));
+    for (int wv = 0; wv < a->waves; wv++) {
+      ref::pick_starts_kernel<<<m, 256>>>(si.as<long long>(), KO, done.as<long long>(), a->starts * a->waves,
+                                          wv * a->starts, a->starts, a->table_len, seg2.as<int2>());
+      ref::gather_kernel<true><<<m, 512, gather_smem(W2, S, a->starts)>>>(
+        seg2.as<int2>(), a->starts, nullptr, a->table_len, tptr.as<long long>(), a->n, sketch.as<signed char>(),
+        nullptr, 1, scale.as<float>(), qs.as<float>(), S, W2, logW2, cand2.as<int>(), dist2.as<float>(),
+        n2.as<int>());
+      ref::rerank_keep_kernel<<<m, 256, D * sizeof(float)>>>(cand2.as<int>(), dist2.as<float>(), n2.as<int>(),
+                                                             W2, xptr.as<long long>(), a->n, D, q.as<float>(),
+                                                             a->wave_rerank, KO, si.as<long long>(),
+                                                             sd.as<float>(), false);
+    }
+    e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
+  cudaMemcpy(a->kept_ids, si.p, sizeof(long long) * m * KO, cudaMemcpyDeviceToHost);
+  cudaMemcpy(a->kept_dist, sd.p, sizeof(float) * m * KO, cudaMemcpyDeviceToHost);
+  e = cudaGetLastError();
+  return static_cast<int>(e);
+}

@@ -8,10 +8,13 @@
 // (distance bits, id) first", which is one of the outcomes the reference allows.
 //
 // Parity pin: the E8 decode and cell code are checked against the reference's own e8.cuh
-// compiled for the host (oracle/_ref, see the Makefile) and against the properties its unit
-// test states (lattice membership, Voronoi optimality, hash_ref). The projection GEMM and the
-// sketch-query GEMM run inside closed vendor libraries in the reference, so their rounding is
-// not reproducible bit for bit: parity there is pinned by tolerance only.
+// compiled for the host and for the GPU (oracle/_ref, see the Makefile) and against the
+// properties its unit test states (lattice membership, Voronoi optimality, hash_ref). The cell
+// lookup, gather, sketch scoring, selection, exact rerank, kept-list merge and start-point choice
+// are checked against the reference's own kernels (search_kernels.cuh compiled unmodified into
+// oracle/_ref/libref_search.so and run on the GPU by tests/test_gpu_reference_kernels.py). The
+// projection GEMM and the sketch-query GEMM run inside closed vendor libraries in the reference,
+// so their rounding is not reproducible bit for bit: parity there is pinned by tolerance only.
 
 #include "octex_oracle.h"
 

@@ -216,7 +216,7 @@ class _RefSearchArgs(C.Structure):
                 ("rerank", C.c_int32), ("wave_rerank", C.c_int32), ("k", C.c_int32),
                 ("seg", C.c_void_p), ("w1", C.c_int32), ("cand1", C.c_void_p), ("dist1", C.c_void_p),
                 ("n1", C.c_void_p), ("kept1_ids", C.c_void_p), ("kept1_dist", C.c_void_p),
-                ("kept_ids", C.c_void_p), ("kept_dist", C.c_void_p)]
+                ("kept_ids", C.c_void_p), ("kept_dist", C.c_void_p), ("kernel_ms", C.c_void_p)]
 
 
 def ref_search():
@@ -229,7 +229,8 @@ def ref_search_pipeline(arrays, meta, y, qs, queries, k=10, *, read=32, starts=1
                         rerank=128, wave_rerank=128):
     """Run the reference's probe / gather / rerank / pick-starts kernels on this machine's GPU on a
     batch whose projected coordinates ``y`` (fp16 bits), sketch-space queries ``qs`` and queries are
-    given.  Returns a dict: seg, cand1, dist1, n1, kept1_ids, kept1_dist, kept_ids, kept_dist."""
+    given.  Returns a dict: seg, cand1, dist1, n1, kept1_ids, kept1_dist, kept_ids, kept_dist, and
+    kernel_ms (device milliseconds of the first round's and of the waves' kernels)."""
     lib_ = ref_search()
     keep = {name: np.ascontiguousarray(arrays[name]) for name in
             ("lists", "keys", "offsets", "base", "sketch_scale", "sketch", "vectors", "table")}
@@ -246,7 +247,8 @@ def ref_search_pipeline(arrays, meta, y, qs, queries, k=10, *, read=32, starts=1
     out = dict(seg=np.zeros((m, C_, 2), np.int32), cand1=np.zeros((m, w1), np.int32),
                dist1=np.zeros((m, w1), np.float32), n1=np.zeros(m, np.int32),
                kept1_ids=np.zeros((m, KO), np.int64), kept1_dist=np.zeros((m, KO), np.float32),
-               kept_ids=np.zeros((m, KO), np.int64), kept_dist=np.zeros((m, KO), np.float32))
+               kept_ids=np.zeros((m, KO), np.int64), kept_dist=np.zeros((m, KO), np.float32),
+               kernel_ms=np.zeros(2, np.float32))
     a = _RefSearchArgs()
     a.n, a.dim, a.copies, a.blocks = meta["n"], meta["dim"], C_, meta["blocks"]
     a.levels, a.list_len, a.log_buckets = len(meta["spacings"]), meta["list_len"], meta["log_buckets"]

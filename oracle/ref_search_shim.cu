@@ -88,6 +88,8 @@ struct ref_search_args {
   float* kept1_dist;
   int64_t* kept_ids;          // [m, KO] after the waves
   float* kept_dist;
+  float* kernel_ms;           // [2] (may be null): device time of the first round's kernels (lookup,
+                              // gather, rerank) and of the waves' kernels, by CUDA events
 };
 
 // Returns 0, a CUDA error code, or -1 for arguments the kernels cannot take.
@@ -128,6 +130,10 @@ extern "C" int ref_search_pipeline(const ref_search_args* a)
   cudaMemset(cand.p, 0xff, sizeof(int) * m * W);
   cudaMemset(dist.p, 0, sizeof(float) * m * W);
 
+  cudaEvent_t ev[4];
+  for (auto& v : ev)
+    cudaEventCreate(&v);
+  cudaEventRecord(ev[0]);
   // cell lookup (search.cu:105-137)
   {
     const int64_t tot = int64_t{m} * C;
@@ -151,6 +157,7 @@ extern "C" int ref_search_pipeline(const ref_search_args* a)
                                                          xptr.as<long long>(), a->n, D, q.as<float>(),
                                                          a->rerank, KO, si.as<long long>(), sd.as<float>(),
                                                          true);
+  cudaEventRecord(ev[1]);
   cudaError_t e = cudaDeviceSynchronize();
   if (e != cudaSuccess) return static_cast<int>(e);
   cudaMemcpy(a->seg, seg.p, sizeof(int2) * m * C, cudaMemcpyDeviceToHost);
@@ -165,6 +172,7 @@ extern "C" int ref_search_pipeline(const ref_search_args* a)
   if (a->waves > 0) {
     cudaFuncSetAttribute(ref::gather_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          static_cast<int>(gather_smem(W2, S, a->starts)));
+    cudaEventRecord(ev[2]);
     for (int wv = 0; wv < a->waves; wv++) {
       ref::pick_starts_kernel<<<m, 256>>>(si.as<long long>(), KO, done.as<long long>(), a->starts * a->waves,
                                           wv * a->starts, a->starts, a->table_len, seg2.as<int2>());
@@ -177,9 +185,17 @@ extern "C" int ref_search_pipeline(const ref_search_args* a)
                                                              a->wave_rerank, KO, si.as<long long>(),
                                                              sd.as<float>(), false);
     }
+    cudaEventRecord(ev[3]);
     e = cudaDeviceSynchronize();
     if (e != cudaSuccess) return static_cast<int>(e);
   }
+  if (a->kernel_ms != nullptr) {
+    a->kernel_ms[0] = a->kernel_ms[1] = 0.f;
+    cudaEventElapsedTime(&a->kernel_ms[0], ev[0], ev[1]);
+    if (a->waves > 0) cudaEventElapsedTime(&a->kernel_ms[1], ev[2], ev[3]);
+  }
+  for (auto& v : ev)
+    cudaEventDestroy(v);
   cudaMemcpy(a->kept_ids, si.p, sizeof(long long) * m * KO, cudaMemcpyDeviceToHost);
   cudaMemcpy(a->kept_dist, sd.p, sizeof(float) * m * KO, cudaMemcpyDeviceToHost);
   e = cudaGetLastError();

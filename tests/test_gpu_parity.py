@@ -322,10 +322,11 @@ def test_dlpack_c_api(gpu_small):
     L.cuvsResourcesDestroy(res)
 
 
-def test_full_size_properties():
+def test_full_size_properties(oracle):
     """Size-independent properties on a larger index built on the GPU (100 000 x 128, the plumbing
     configuration with fewer copies): distances ascending, ids distinct and in range, every distance
-    equal to the exact fp32 distance to the stored fp16 row, and recall against brute force."""
+    equal to the exact fp32 distance to the stored fp16 row, recall against brute force, and the
+    neighbours the reference's own kernels find from the same projected coordinates."""
     import torch
     from octex_b200 import build_index, synth
     base = synth.plumbing(100000, 128, seed=0)
@@ -347,6 +348,21 @@ def test_full_size_properties():
     r = recall(ids, truth)
     print(f"recall@10 {r:.4f} (read 32, starts 128, waves 3, rerank 256, 24 copies)")
     assert r >= 0.95
+    # the reference's kernels (oracle/_ref/libref_search.so) on the same batch: the tensor-core
+    # projection's coordinates go in, their neighbours must be these neighbours
+    if oracle.ref_search() is not None:
+        kw = dict(read=16, starts=32, waves=2, rerank=128, wave_rerank=256)
+        idx.set_debug(taps=True)
+        dist, ids = idx.search(queries, 10, **kw)
+        y = idx.fetch("y", np.uint16, (len(queries), -1))
+        qs = idx.fetch("qs", np.float32, (len(queries), -1))
+        host = {k_: v_.cpu().numpy() for k_, v_ in arrays.items()}
+        ref = oracle.ref_search_pipeline(host, meta, y, qs, queries, 10, **kw)
+        agree = float((ref["kept_ids"][:, :10] == ids).mean())
+        print(f"ids equal to the reference kernels' on {agree:.5f} of the slots")
+        assert agree >= 0.999
+        same = ref["kept_ids"][:, :10] == ids
+        np.testing.assert_allclose(ref["kept_dist"][:, :10][same], dist[same], rtol=1e-4, atol=1e-3)
     idx.close()
 
 

@@ -214,9 +214,11 @@ class _RefSearchArgs(C.Structure):
                 ("m", C.c_int32), ("y", C.c_void_p), ("qs", C.c_void_p), ("q", C.c_void_p),
                 ("read", C.c_int32), ("starts", C.c_int32), ("waves", C.c_int32),
                 ("rerank", C.c_int32), ("wave_rerank", C.c_int32), ("k", C.c_int32),
+                ("sketch_rank", C.c_int32), ("final_rerank", C.c_int32),
                 ("seg", C.c_void_p), ("w1", C.c_int32), ("cand1", C.c_void_p), ("dist1", C.c_void_p),
                 ("n1", C.c_void_p), ("kept1_ids", C.c_void_p), ("kept1_dist", C.c_void_p),
-                ("kept_ids", C.c_void_p), ("kept_dist", C.c_void_p), ("kernel_ms", C.c_void_p)]
+                ("kept_ids", C.c_void_p), ("kept_dist", C.c_void_p),
+                ("best_ids", C.c_void_p), ("best_dist", C.c_void_p), ("kernel_ms", C.c_void_p)]
 
 
 def ref_search():
@@ -226,11 +228,11 @@ def ref_search():
 
 
 def ref_search_pipeline(arrays, meta, y, qs, queries, k=10, *, read=32, starts=128, waves=2,
-                        rerank=128, wave_rerank=128):
+                        rerank=128, wave_rerank=128, sketch_rank=False, final_rerank=32):
     """Run the reference's probe / gather / rerank / pick-starts kernels on this machine's GPU on a
     batch whose projected coordinates ``y`` (fp16 bits), sketch-space queries ``qs`` and queries are
-    given.  Returns a dict: seg, cand1, dist1, n1, kept1_ids, kept1_dist, kept_ids, kept_dist, and
-    kernel_ms (device milliseconds of the first round's and of the waves' kernels)."""
+    given.  Returns a dict: seg, cand1, dist1, n1, kept1_ids, kept1_dist, kept_ids, kept_dist, best_ids, best_dist (the
+    search result) and kernel_ms (device milliseconds of the first round's and of the waves' kernels)."""
     lib_ = ref_search()
     keep = {name: np.ascontiguousarray(arrays[name]) for name in
             ("lists", "keys", "offsets", "base", "sketch_scale", "sketch", "vectors", "table")}
@@ -248,6 +250,7 @@ def ref_search_pipeline(arrays, meta, y, qs, queries, k=10, *, read=32, starts=1
                dist1=np.zeros((m, w1), np.float32), n1=np.zeros(m, np.int32),
                kept1_ids=np.zeros((m, KO), np.int64), kept1_dist=np.zeros((m, KO), np.float32),
                kept_ids=np.zeros((m, KO), np.int64), kept_dist=np.zeros((m, KO), np.float32),
+               best_ids=np.zeros((m, k), np.int64), best_dist=np.zeros((m, k), np.float32),
                kernel_ms=np.zeros(2, np.float32))
     a = _RefSearchArgs()
     a.n, a.dim, a.copies, a.blocks = meta["n"], meta["dim"], C_, meta["blocks"]
@@ -261,6 +264,7 @@ def ref_search_pipeline(arrays, meta, y, qs, queries, k=10, *, read=32, starts=1
         setattr(a, field, keep[name].ctypes.data)
     a.m, a.y, a.qs, a.q = m, y.ctypes.data, qs.ctypes.data, q.ctypes.data
     a.read, a.starts, a.waves, a.rerank, a.wave_rerank, a.k = read, starts, waves, rerank, wave_rerank, k
+    a.sketch_rank, a.final_rerank = int(sketch_rank), final_rerank
     a.w1 = w1
     for name, arr in out.items():
         setattr(a, name, arr.ctypes.data)

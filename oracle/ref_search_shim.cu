@@ -1,6 +1,7 @@
 // TEST INFRASTRUCTURE ONLY. The reference's own search kernels
 // (cpp/src/neighbors/octex/detail/search_kernels.cuh of hpdic/octex: probe_kernel, gather_kernel,
-// rerank_keep_kernel, pick_starts_kernel) compiled unmodified as device code and launched with the
+// rerank_keep_kernel, sketch_keep_kernel, pick_starts_kernel, final_rerank_kernel, take_k_kernel)
+// compiled unmodified as device code and launched with the
 // launch shapes of the reference's search.cu (:344-357, :393, :433-450, :453, :488), behind one
 // host function with host pointers in and out. A GPU test feeds it the projected coordinates,
 // sketch-space queries and queries of a batch and compares what the reference's kernels make of
@@ -78,6 +79,7 @@ struct ref_search_args {
   const float* q;             // [m, dim] uncentred queries
   // parameters
   int32_t read, starts, waves, rerank, wave_rerank, k;
+  int32_t sketch_rank, final_rerank;  // rank by sketch distance; exact rerank of the first final_rerank kept
   // results
   int32_t* seg;               // [m, copies, 2]
   int32_t w1;                 // capacity of cand1 / dist1 per query (>= the hash set of round 1)
@@ -88,6 +90,8 @@ struct ref_search_args {
   float* kept1_dist;
   int64_t* kept_ids;          // [m, KO] after the waves
   float* kept_dist;
+  int64_t* best_ids;          // [m, k] the search result (take_k or final_rerank)
+  float* best_dist;
   float* kernel_ms;           // [2] (may be null): device time of the first round's kernels (lookup,
                               // gather, rerank) and of the waves' kernels, by CUDA events
 };
@@ -101,6 +105,9 @@ extern "C" int ref_search_pipeline(const ref_search_args* a)
   const int64_t T1 = (int64_t{1} << a->log_buckets) + 1;
   if (a->blocks != 2 && a->blocks != 4) return -1;
   if (a->rerank > ref::kMaxRerank || a->wave_rerank > ref::kMaxRerank) return -1;
+  const int FR = std::min(a->final_rerank, KO);
+  if (a->sketch_rank && (KO > ref::kMaxSketchKO || (FR > 0 && (a->k > FR || FR > ref::kMaxRerank)))) return -1;
+  if (a->k > KO) return -1;
   if (KO + std::max(a->rerank, a->wave_rerank) > ref::kMaxKeepSort) return -1;
   const int logW = hash_log_for(int64_t{C} * lr), W = 1 << logW;
   if (a->w1 < W) return -1;
@@ -120,12 +127,13 @@ extern "C" int ref_search_pipeline(const ref_search_args* a)
     seg2(nullptr, sizeof(int2) * m * std::max(a->starts, 1)),
     cand2(nullptr, sizeof(int) * m * W2), dist2(nullptr, sizeof(float) * m * W2),
     n2(nullptr, sizeof(int) * m),
-    done(nullptr, sizeof(long long) * m * std::max(a->starts * a->waves, 1));
+    done(nullptr, sizeof(long long) * m * std::max(a->starts * a->waves, 1)),
+    bi(nullptr, sizeof(long long) * m * a->k), bd(nullptr, sizeof(float) * m * a->k);
   const long long xp = reinterpret_cast<long long>(vectors.p), tp = reinterpret_cast<long long>(table.p);
   device_array xptr(&xp, sizeof(xp)), tptr(&tp, sizeof(tp));
   for (const device_array* d : {&inv_f, &lists, &keys, &offsets, &base, &scale, &sketch, &vectors, &table,
                                 &y, &qs, &q, &seg, &cand, &dist, &nin, &si, &sd, &seg2, &cand2, &dist2,
-                                &n2, &done, &xptr, &tptr})
+                                &n2, &done, &bi, &bd, &xptr, &tptr})
     if (d->err != cudaSuccess) return static_cast<int>(d->err);
   cudaMemset(cand.p, 0xff, sizeof(int) * m * W);
   cudaMemset(dist.p, 0, sizeof(float) * m * W);
@@ -153,10 +161,14 @@ extern "C" int ref_search_pipeline(const ref_search_args* a)
   ref::gather_kernel<false><<<m, 256, gather_smem(W, S, C)>>>(
     seg.as<int2>(), C, lists.as<int>(), a->stride, nullptr, 1, sketch.as<signed char>(), nullptr, 1,
     scale.as<float>(), qs.as<float>(), S, W, logW, cand.as<int>(), dist.as<float>(), nin.as<int>());
-  ref::rerank_keep_kernel<<<m, 256, D * sizeof(float)>>>(cand.as<int>(), dist.as<float>(), nin.as<int>(), W,
-                                                         xptr.as<long long>(), a->n, D, q.as<float>(),
-                                                         a->rerank, KO, si.as<long long>(), sd.as<float>(),
-                                                         true);
+  if (a->sketch_rank)  // search.cu:384
+    ref::sketch_keep_kernel<<<m, 512>>>(cand.as<int>(), dist.as<float>(), nin.as<int>(), W, KO,
+                                        si.as<long long>(), sd.as<float>(), true);
+  else
+    ref::rerank_keep_kernel<<<m, 256, D * sizeof(float)>>>(cand.as<int>(), dist.as<float>(), nin.as<int>(), W,
+                                                           xptr.as<long long>(), a->n, D, q.as<float>(),
+                                                           a->rerank, KO, si.as<long long>(), sd.as<float>(),
+                                                           true);
   cudaEventRecord(ev[1]);
   cudaError_t e = cudaDeviceSynchronize();
   if (e != cudaSuccess) return static_cast<int>(e);
@@ -180,10 +192,14 @@ extern "C" int ref_search_pipeline(const ref_search_args* a)
         seg2.as<int2>(), a->starts, nullptr, a->table_len, tptr.as<long long>(), a->n, sketch.as<signed char>(),
         nullptr, 1, scale.as<float>(), qs.as<float>(), S, W2, logW2, cand2.as<int>(), dist2.as<float>(),
         n2.as<int>());
-      ref::rerank_keep_kernel<<<m, 256, D * sizeof(float)>>>(cand2.as<int>(), dist2.as<float>(), n2.as<int>(),
-                                                             W2, xptr.as<long long>(), a->n, D, q.as<float>(),
-                                                             a->wave_rerank, KO, si.as<long long>(),
-                                                             sd.as<float>(), false);
+      if (a->sketch_rank)  // search.cu:479
+        ref::sketch_keep_kernel<<<m, 512>>>(cand2.as<int>(), dist2.as<float>(), n2.as<int>(), W2, KO,
+                                            si.as<long long>(), sd.as<float>(), false);
+      else
+        ref::rerank_keep_kernel<<<m, 256, D * sizeof(float)>>>(cand2.as<int>(), dist2.as<float>(), n2.as<int>(),
+                                                               W2, xptr.as<long long>(), a->n, D, q.as<float>(),
+                                                               a->wave_rerank, KO, si.as<long long>(),
+                                                               sd.as<float>(), false);
     }
     cudaEventRecord(ev[3]);
     e = cudaDeviceSynchronize();
@@ -198,6 +214,18 @@ extern "C" int ref_search_pipeline(const ref_search_args* a)
     cudaEventDestroy(v);
   cudaMemcpy(a->kept_ids, si.p, sizeof(long long) * m * KO, cudaMemcpyDeviceToHost);
   cudaMemcpy(a->kept_dist, sd.p, sizeof(float) * m * KO, cudaMemcpyDeviceToHost);
+  // the result (search.cu:503-517)
+  if (a->sketch_rank && FR > 0)
+    ref::final_rerank_kernel<<<m, 256, D * sizeof(float)>>>(si.as<long long>(), KO, FR, xptr.as<long long>(), a->n,
+                                                            D, q.as<float>(), a->k, bi.as<long long>(),
+                                                            bd.as<float>());
+  else
+    ref::take_k_kernel<<<static_cast<unsigned>((int64_t{m} * a->k + 255) / 256), 256>>>(
+      si.as<long long>(), sd.as<float>(), KO, a->k, m, bi.as<long long>(), bd.as<float>());
+  e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return static_cast<int>(e);
+  cudaMemcpy(a->best_ids, bi.p, sizeof(long long) * m * a->k, cudaMemcpyDeviceToHost);
+  cudaMemcpy(a->best_dist, bd.p, sizeof(float) * m * a->k, cudaMemcpyDeviceToHost);
   e = cudaGetLastError();
   return static_cast<int>(e);
 }

@@ -1,7 +1,7 @@
 """The CPU checker against the reference's own search kernels run on this GPU.
 
 oracle/_ref/libref_search.so holds probe_kernel, gather_kernel, rerank_keep_kernel and
-pick_starts_kernel of the reference (cpp/src/neighbors/octex/detail/search_kernels.cuh), compiled
+pick_starts_kernel, sketch_keep_kernel, final_rerank_kernel and take_k_kernel of the reference (cpp/src/neighbors/octex/detail/search_kernels.cuh), compiled
 unmodified and launched with the shapes of its search.cu.  Fed the same projected coordinates,
 sketch-space queries and queries, the reference's kernels and the checker must agree: segments and
 candidate sets exactly, sketch and exact distances to the last bits the different summation orders
@@ -21,6 +21,8 @@ pytestmark = pytest.mark.gpu
     dict(read=8, starts=32, waves=2, rerank=64, wave_rerank=64),
     dict(read=16, starts=24, waves=1, rerank=128, wave_rerank=200),
     dict(read=4, starts=16, waves=0, rerank=32),
+    dict(read=8, starts=64, waves=2, sketch_rank=True, final_rerank=32),
+    dict(read=8, starts=48, waves=1, sketch_rank=True, final_rerank=0),
 ])
 def test_checker_matches_reference_kernels(oracle, small_index, wide_index, which, kw):
     if oracle.ref_search() is None:
@@ -38,9 +40,15 @@ def test_checker_matches_reference_kernels(oracle, small_index, wide_index, whic
     full = dict(rerank=128, wave_rerank=128)
     full.update(kw)
     ref = oracle.ref_search_pipeline(arrays, meta, y, qs, queries, 10, **full)
-    KO = max(kw["starts"], 10)  # with k = KO the checker's results are its whole final kept list
-    want_ids, want_dist, t = oracle.Index(arrays, meta).search(
-        queries, KO, y_in=y, taps=("seg", "cand1", "kept1_ids", "kept1_dist"), **kw)
+    best_ids, best_dist, t = oracle.Index(arrays, meta).search(
+        queries, 10, y_in=y, taps=("seg", "cand1", "kept1_ids", "kept1_dist"), **kw)
+    stages = [(ref["kept1_ids"], ref["kept1_dist"], t["kept1_ids"], t["kept1_dist"]),
+              (ref["best_ids"], ref["best_dist"], best_ids, best_dist)]
+    if not kw.get("sketch_rank"):
+        # with k = KO the checker's result is its whole final kept list
+        KO = max(kw["starts"], 10)
+        want_ids, want_dist, _ = oracle.Index(arrays, meta).search(queries, KO, y_in=y, **kw)
+        stages.append((ref["kept_ids"], ref["kept_dist"], want_ids, want_dist))
 
     # cell lookup: identical segments
     assert np.array_equal(ref["seg"], t["seg"]), "segments"
@@ -56,8 +64,7 @@ def test_checker_matches_reference_kernels(oracle, small_index, wide_index, whic
     assert worst < 1e-5, worst
     # kept lists after the first round and after the waves: the same ids up to near-ties of the
     # distances (summation orders differ), distances within 1e-5 relative
-    for got_i, got_d, want_i, want_d in ((ref["kept1_ids"], ref["kept1_dist"], t["kept1_ids"], t["kept1_dist"]),
-                                         (ref["kept_ids"], ref["kept_dist"], want_ids, want_dist)):
+    for got_i, got_d, want_i, want_d in stages:
         # rows with the same ids in the same order: distances to the last bits of the summation
         rows = (got_i == want_i).all(axis=1)
         assert rows.mean() > 0.9, float(rows.mean())

@@ -192,7 +192,11 @@ OCTEX_B200_EXPORT cuvsError_t octexB200LoadRank(cuvsResources_t res, const char*
  * calls the search with the same queries and parameters and receives all results:
  * replicate placement answers a slice of each batch per process, shard placement runs the first
  * round of all rows over the process's copies, exchanges the kept lists (NCCL send / receive),
- * and runs the waves on the process's slice; an NCCL all-gather brings the slices together. */
+ * and runs the waves on the process's slice; an NCCL all-gather brings the slices together.
+ * octexB200CommInit is also where arrays dealt by rows (the neighbor table under shard placement,
+ * shard_vectors, sketch = SHARD: cpp/src/neighbors/octex/load.cu:315,406-427) become whole: every
+ * process publishes a CUDA IPC handle of the row range it holds and maps the others' ranges, which
+ * the kernels then read with plain loads. A search before this call fails and says so. */
 OCTEX_B200_EXPORT cuvsError_t octexB200CommUniqueId(void* id128);
 OCTEX_B200_EXPORT cuvsError_t octexB200CommInit(cuvsOctexIndex_t index, const void* id128);
 

@@ -63,6 +63,13 @@ LADDER = [
 NCU_TRAFFIC = {"round_rows": 1.225e9, "round_lists": 0.681e9}
 
 
+def given_search(args):
+    """--search JSON over the defaults of search_params (cpp/include/cuvs/neighbors/octex.hpp:101-135)."""
+    sp = dict(read=32, starts=128, waves=2, rerank=128, wave_rerank=128)
+    sp.update(json.loads(args.search))
+    return sp
+
+
 def log(*a):
     print(*a, file=sys.stderr, flush=True)
 
@@ -179,7 +186,7 @@ def run_reference(args, rank, world):
     dev = "cuda" if torch.cuda.is_available() else "cpu"
     arrays, meta = build_index.build_arrays(base, build_index.IndexParams(**w["build"]), device=dev)
     ox = oracle_py.Index(arrays, meta)
-    sp = json.loads(args.search) if args.search else dict(LADDER[args.ladder_start])
+    sp = given_search(args) if args.search else dict(LADDER[args.ladder_start])
     sample = queries[:args.cpu_sample]
     cores = os.cpu_count() or 1
     for _ in range(max(args.warmup, 1)):
@@ -253,7 +260,7 @@ def main():
 
     # search parameters: the cheapest rung of the ladder that reaches recall@10 >= 0.99
     chosen, rec = None, 0.0
-    for sp in ([json.loads(args.search)] if args.search else LADDER[args.ladder_start:]):
+    for sp in ([given_search(args)] if args.search else LADDER[args.ladder_start:]):
         _, ids = idx.search(q_dev, K, **sp)
         r = recall_of(ids.cpu().numpy(), truth)
         log(f"[rank {rank}] {sp} recall@10 {r:.4f}")

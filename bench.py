@@ -163,7 +163,9 @@ def algorithmic_bytes(stats, sp, meta, k):
     r1 = np.minimum(n1, sp["rerank"])  # the first round starts from an empty kept list
     waves = sp["waves"]
     lists = (4 * stats[:, 2] + n1 * S + r1 * 2 * D + 4 * D + 4 * S + KO * 12).sum()
-    out = {"probe": int((stats[:, 0] * 16 + stats[:, 1] * 8).sum()),
+    pairs = len(stats) * meta["copies"]
+    # 16-byte table slots examined, plus the codes read and the segment written per (query, copy)
+    out = {"probe": int((stats[:, 1] * 16).sum() + pairs * (8 * len(meta["spacings"]) + 8)),
            "round_lists": int(lists)}
     if waves:
         rerank_w = stats[:, 7] - r1  # rows the waves read (ids already kept are not read again)

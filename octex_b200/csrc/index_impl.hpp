@@ -3,8 +3,13 @@
 // Layout (the reference's is in cpp/src/neighbors/octex/detail/index_impl.hpp:115-177 of
 // hpdic/octex; differences are marked *):
 //   lists   i32 [Cg, stride]     cell rows of list_len ids, nearest to the cell centre first
-//   keys    i64 [Cg, L, mmax]    cell codes in (bucket, code) order
-//   offsets i32 [Cg, L, T + 1]   CSR bounds of the buckets into keys
+// * cell_table {i64 key, i32 row, pad} [sum of the (copy, level) table sizes]: the cells of every
+//                                (copy, level) in an open-addressing table at most half full (slot =
+//                                low bits of the code, linear probing), with cell_off i64 [Cg, L]
+//                                (first slot) and cell_mask i32 [Cg, L] (slots - 1). Built at placement
+//                                from the directory's keys i64 [C, L, mmax] and the cell counts in its
+//                                offsets i32 [C, L, T + 1]; the reference keeps those two arrays on the
+//                                GPU and walks a bucket of keys per lookup
 //   base    i32 [Cg, L]          first list row of a level inside the copy
 // * ut      f16 [Cg * 8b, ldu]   projections, one row per projected coordinate, K-major
 //                                (ldu = dim rounded up to 64, zero padded): the operand layout of
@@ -58,8 +63,8 @@ struct device_part {
   int64_t stride = 0;
   int64_t mmax   = 0;
   int ldu        = 0;
-  dbuf lists, keys, offsets, base, ut, shift, inv_f, mean, basis, scale, sketch, vectors, table,
-    level_on;
+  dbuf lists, base, ut, shift, inv_f, mean, basis, scale, sketch, vectors, table, level_on;
+  dbuf cell_table, cell_off, cell_mask;  // open-addressing table of the cells of every (copy, level)
   dealt_rows table_rows, sketch_rows, vector_rows;
   cudaStream_t stream = nullptr;
   int64_t bytes       = 0;

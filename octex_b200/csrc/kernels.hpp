@@ -67,11 +67,28 @@ void project_decode_tc(const project_tc_plan& p, int L, const __half* shift, con
 void cell_codes_f32(const float* y, int64_t n, int blocks, float inv_f, long long* codes,
                     cudaStream_t s);
 
+/// One slot of the cell table of a (copy, level): the 64-bit code of a cell and the row of its list
+/// among the level's cells (-1: empty slot). 16 bytes: a lookup reads one 32-byte sector, where the
+/// reference's bucket array plus key array (detail/search_kernels.cuh:100-126) costs two dependent
+/// ones.
+struct cell_slot {
+  long long key;
+  int row;
+  int pad;
+};
+
+/// Fill the open-addressing tables of CL (copy, level) pairs from their key arrays: pair cl holds
+/// ncells[cl] codes keys[cl * mmax + p], p = row of the cell; its table is table + toff[cl],
+/// tmask[cl] + 1 slots (a power of two, at least twice the cells), home slot = low bits of the code.
+/// The table must be filled with 0xff bytes before (row -1 everywhere).
+void build_cell_tables(const long long* keys, int64_t mmax, const int* ncells, const long long* toff,
+                       const int* tmask, int CL, cell_slot* table, cudaStream_t s);
+
 /// seg [m, C] = (first list entry, entries read) of the finest level whose cell holds a list,
-/// (0, 0) when none does. stats (may be null) [m, 2] += (levels tried, keys scanned).
-void probe(const long long* codes, int m, int C, int L, const int* offsets, int64_t T1,
-           const long long* keys, int64_t mmax, const int* base, const unsigned char* level_on,
-           int list_len, int lr, int log_buckets, int2* seg, long long* stats, cudaStream_t s);
+/// (0, 0) when none does. stats (may be null) [m, 2] += (levels tried, table slots examined).
+void probe(const long long* codes, int m, int C, int L, const cell_slot* table, const long long* toff,
+           const int* tmask, const int* base, const unsigned char* level_on, int list_len, int lr,
+           int2* seg, long long* stats, cudaStream_t s);
 
 /// Where the rows of an array live when they are dealt over the GPUs in ranges of `rows`
 /// (ptrs[g] = start of rows [g * rows, (g + 1) * rows) in that GPU's memory, mapped into this

@@ -6,6 +6,7 @@
 // preparation of the projection (fp16, here K-major for the tensor-core kernel) are the same.
 
 #include "index_impl.hpp"
+#include "kernels.hpp"
 #include "npy.hpp"
 
 #include <cuda_fp16.h>
@@ -216,21 +217,50 @@ void place(index_impl& ix, source_arrays const& src)
     }
   }
   p.mmax = a.mmax;
-  put(p.keys, a.keys, static_cast<size_t>(L) * p.mmax * sizeof(int64_t));
-  put(p.offsets, a.offsets, static_cast<size_t>(L) * T1 * sizeof(int32_t));
   put(p.base, a.base, static_cast<size_t>(L) * sizeof(int32_t));
 
-  // which levels of which copies hold cells: the last CSR bound of a level is its cell count
+  // The cells of every (copy, level). The directory holds them as CSR bucket bounds over sorted
+  // keys (offsets [C, L, T + 1], keys [C, L, mmax]: build.cu:215-349 of the reference); the kernels
+  // here look them up in one open-addressing table per (copy, level), slot = (key, row of the
+  // cell), at most half full, built on the GPU from the keys. The last CSR bound of a level is its
+  // cell count; the bucket bounds themselves never go to the GPU.
   {
-    std::vector<unsigned char> on(static_cast<size_t>(Cg) * L);
+    const int CL = Cg * L;
+    std::vector<int> ncells(CL), mask(CL);
+    std::vector<long long> off(CL);
+    std::vector<unsigned char> on(static_cast<size_t>(CL));
+    long long slots = 0;
     for (int c = 0; c < Cg; c++)
       for (int j = 0; j < L; j++) {
         int32_t last = 0;
         st.fetch(&last, a.offsets + (int64_t{cl[c]} * L + j) * T1 + (T1 - 1), sizeof(int32_t));
-        on[c * L + j] = last > 0;
+        OCTEX_EXPECTS(last >= 0 && last <= p.mmax, "octex: a level's cell count exceeds its key array");
+        const int k = c * L + j;
+        ncells[k]   = last;
+        on[k]       = last > 0;
+        int cap     = 4;
+        while (cap < 2 * last)
+          cap <<= 1;
+        mask[k] = cap - 1;
+        off[k]  = slots;
+        slots += cap;
       }
     own(p.level_on, on.size());
     st.copy(p.level_on.ptr, on.data(), on.size());
+    own(p.cell_off, sizeof(long long) * CL);
+    st.copy(p.cell_off.ptr, off.data(), p.cell_off.size);
+    own(p.cell_mask, sizeof(int) * CL);
+    st.copy(p.cell_mask.ptr, mask.data(), p.cell_mask.size);
+    own(p.cell_table, sizeof(kernels::cell_slot) * static_cast<size_t>(slots));
+    OCTEX_CUDA_TRY(cudaMemsetAsync(p.cell_table.ptr, 0xff, p.cell_table.size, p.stream));
+    // the keys of this process's copies on the GPU for the duration of the build
+    dbuf keys, counts(p.device, sizeof(int) * CL);
+    const int64_t before = p.bytes;
+    put(keys, a.keys, static_cast<size_t>(L) * p.mmax * sizeof(int64_t));
+    p.bytes = before;  // not kept
+    st.copy(counts.ptr, ncells.data(), counts.size);
+    kernels::build_cell_tables(keys.as<long long>(), p.mmax, counts.as<int>(), p.cell_off.as<long long>(),
+                               p.cell_mask.as<int>(), CL, p.cell_table.as<kernels::cell_slot>(), p.stream);
     OCTEX_CUDA_TRY(cudaStreamSynchronize(p.stream));
   }
 

@@ -227,74 +227,95 @@ __global__ void cell_codes_f32_kernel(const float* __restrict__ y, int64_t n, fl
 
 // ---- cell lookup -----------------------------------------------------------------------------
 
+// The cells of a (copy, level) in an open-addressing table (slot = low bits of the 64-bit code,
+// linear probing): what the reference keeps as a bucket-bound array plus a key array
+// (search_kernels.cuh:100-126), re-laid so that a lookup costs one random 32-byte sector instead of
+// two dependent ones. Built once when the index is placed.
+__global__ void fill_cell_tables_kernel(const long long* __restrict__ keys,
+                                        int64_t mmax,
+                                        const int* __restrict__ ncells,
+                                        const long long* __restrict__ toff,
+                                        const int* __restrict__ tmask,
+                                        cell_slot* __restrict__ table)
+{
+  const int cl = blockIdx.y;
+  const int p  = blockIdx.x * blockDim.x + threadIdx.x;
+  if (p >= ncells[cl]) return;
+  const long long key = keys[static_cast<int64_t>(cl) * mmax + p];
+  const unsigned mask = static_cast<unsigned>(tmask[cl]);
+  cell_slot* mine     = table + toff[cl];
+  unsigned s          = static_cast<unsigned>(key) & mask;
+  for (unsigned probe = 0; probe <= mask; probe++) {
+    if (atomicCAS(&mine[s].row, -1, p) == -1) {
+      mine[s].key = key;  // nobody reads the table before this kernel is over
+      return;
+    }
+    s = (s + 1) & mask;
+  }
+}
+
 // search_kernels.cuh:100-126: the finest level whose cell holds a list. One thread per
-// (query, copy). The codes of all levels are already there, so the bucket bounds of every level
-// are fetched at once, then the first key of every non-empty bucket at once: two memory round
-// trips for the common case instead of two per level tried. The answer and the counters are those
-// of the level-by-level walk.
+// (query, copy). The codes of all levels are already there, so the home slot of every level is
+// fetched at once (one 16-byte load each): one memory round trip for the common case instead of
+// two per level tried. The answer is that of the level-by-level walk.
 constexpr int kProbeLevels = 8;  // levels handled in one sweep; more are walked in further sweeps
 __global__ void probe_kernel(const long long* __restrict__ codes,
                              int64_t pairs,
                              int C,
                              int L,
-                             const int* __restrict__ offsets,
-                             int64_t T1,
-                             const long long* __restrict__ keys,
-                             int64_t mmax,
+                             const cell_slot* __restrict__ table,
+                             const long long* __restrict__ toff,
+                             const int* __restrict__ tmask,
                              const int* __restrict__ base,
                              const unsigned char* __restrict__ level_on,
                              int list_len,
                              int lr,
-                             int log_buckets,
                              int2* __restrict__ seg,
                              long long* __restrict__ stats)
 {
   const int64_t t = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (t >= pairs) return;
-  const int c           = static_cast<int>(t % C);
-  const long long bmask = (1LL << log_buckets) - 1;
-  int2 sg               = make_int2(0, 0);
+  const int c = static_cast<int>(t % C);
+  int2 sg     = make_int2(0, 0);
   long long tried = 0, scanned = 0;
   bool found = false;
   for (int j0 = 0; j0 < L && !found; j0 += kProbeLevels) {
-    long long h[kProbeLevels], k0[kProbeLevels];
-    int lo[kProbeLevels], hi[kProbeLevels];
+    long long h[kProbeLevels];
+    int4 first[kProbeLevels];  // the home slot: (key low, key high, row, pad)
+    bool on[kProbeLevels];
 #pragma unroll
     for (int u = 0; u < kProbeLevels; u++) {
       const int j = j0 + u;
-      lo[u] = hi[u] = 0;
-      h[u]          = 0;
-      if (j < L && (level_on == nullptr || level_on[c * L + j])) {
+      on[u]       = j < L && (level_on == nullptr || level_on[c * L + j]);
+      h[u]        = 0;
+      first[u]    = make_int4(0, 0, -1, 0);
+      if (on[u]) {
+        const int cl = c * L + j;
         h[u]         = codes[t * L + j];
-        const int* o = offsets + (static_cast<int64_t>(c) * L + j) * T1 + static_cast<int>(h[u] & bmask);
-        lo[u]        = __ldg(o);
-        hi[u]        = __ldg(o + 1);
-        if (hi[u] <= lo[u]) hi[u] = lo[u] - 1;  // mark "tried, empty bucket"
-      } else {
-        hi[u] = lo[u] - 2;  // not a level to try
+        first[u]     = __ldg(reinterpret_cast<const int4*>(table + toff[cl] +
+                                                       (static_cast<unsigned>(h[u]) & static_cast<unsigned>(tmask[cl]))));
       }
     }
 #pragma unroll
     for (int u = 0; u < kProbeLevels; u++) {
-      k0[u] = 0;
-      if (hi[u] > lo[u])
-        k0[u] = __ldg(keys + (static_cast<int64_t>(c) * L + j0 + u) * mmax + lo[u]);
-    }
-#pragma unroll
-    for (int u = 0; u < kProbeLevels; u++) {
-      if (found || hi[u] == lo[u] - 2) continue;
+      if (found || !on[u]) continue;
       tried++;
-      if (hi[u] < lo[u]) continue;  // empty bucket
-      const int64_t cl    = static_cast<int64_t>(c) * L + j0 + u;
-      const long long* kk = keys + cl * mmax;
-      for (int p = lo[u]; p < hi[u]; p++) {
+      const int cl        = c * L + j0 + u;
+      const unsigned mask = static_cast<unsigned>(tmask[cl]);
+      const cell_slot* tb = table + toff[cl];
+      unsigned s          = static_cast<unsigned>(h[u]) & mask;
+      int4 e              = first[u];
+      for (unsigned probe = 0; probe <= mask; probe++) {
         scanned++;
-        const long long key = p == lo[u] ? k0[u] : __ldg(kk + p);
+        if (e.z < 0) break;  // an empty slot ends the run: the cell does not exist
+        const long long key = (static_cast<long long>(e.y) << 32) | static_cast<unsigned>(e.x);
         if (key == h[u]) {
-          sg    = make_int2((base[cl] + p) * list_len, lr);
+          sg    = make_int2((base[cl] + e.z) * list_len, lr);
           found = true;
           break;
         }
+        s = (s + 1) & mask;
+        e = __ldg(reinterpret_cast<const int4*>(tb + s));
       }
     }
   }
@@ -389,15 +410,22 @@ void cell_codes_f32(const float* y, int64_t n, int blocks, float inv_f, long lon
   }
 }
 
-void probe(const long long* codes, int m, int C, int L, const int* offsets, int64_t T1,
-           const long long* keys, int64_t mmax, const int* base, const unsigned char* level_on,
-           int list_len, int lr, int log_buckets, int2* seg, long long* stats, cudaStream_t s)
+void build_cell_tables(const long long* keys, int64_t mmax, const int* ncells, const long long* toff,
+                       const int* tmask, int CL, cell_slot* table, cudaStream_t s)
+{
+  if (CL <= 0 || mmax <= 0) return;
+  dim3 grid(blocks_for(mmax, 256), static_cast<unsigned>(CL));
+  fill_cell_tables_kernel<<<grid, 256, 0, s>>>(keys, mmax, ncells, toff, tmask, table);
+}
+
+void probe(const long long* codes, int m, int C, int L, const cell_slot* table, const long long* toff,
+           const int* tmask, const int* base, const unsigned char* level_on, int list_len, int lr,
+           int2* seg, long long* stats, cudaStream_t s)
 {
   const int64_t pairs = static_cast<int64_t>(m) * C;
   if (pairs <= 0) return;
-  probe_kernel<<<blocks_for(pairs, 256), 256, 0, s>>>(codes, pairs, C, L, offsets, T1, keys, mmax,
-                                                      base, level_on, list_len, lr, log_buckets,
-                                                      seg, stats);
+  probe_kernel<<<blocks_for(pairs, 256), 256, 0, s>>>(codes, pairs, C, L, table, toff, tmask, base, level_on,
+                                                      list_len, lr, seg, stats);
 }
 
 void take_k(const long long* si, const float* sd, int KO, int k, int m, long long* bi, float* bd,

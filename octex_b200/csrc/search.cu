@@ -123,7 +123,6 @@ void run_batch(index_impl const& ix, plan& pl, cudaStream_t s, std::vector<cudaE
   const int sw   = ix.sketch_width;
   const int L    = static_cast<int>(ix.spacings.size());
   const int wdt  = 8 * ix.blocks * p.copies;
-  const int64_t T1 = (int64_t{1} << ix.log_buckets) + 1;
   if (pl.stats.ptr != nullptr) {
     OCTEX_CUDA_TRY(cudaMemsetAsync(pl.stats.ptr, 0, pl.stats.size, s));
     OCTEX_CUDA_TRY(cudaMemsetAsync(pl.phase1.ptr, 0, pl.phase1.size, s));
@@ -151,9 +150,10 @@ void run_batch(index_impl const& ix, plan& pl, cudaStream_t s, std::vector<cudaE
                           p.inv_f.as<float>(), levels, pl.codes.as<long long>(), s);
   }
   mark();
-  kernels::probe(pl.codes.as<long long>(), pl.m1, p.copies, L, p.offsets.as<int>(), T1,
-                 p.keys.as<long long>(), p.mmax, p.base.as<int>(), p.level_on.as<unsigned char>(),
-                 ix.list_len, pl.lr, ix.log_buckets, pl.seg.as<int2>(), pl.stats.as<long long>(), s);
+  kernels::probe(pl.codes.as<long long>(), pl.m1, p.copies, L, p.cell_table.as<kernels::cell_slot>(),
+                 p.cell_off.as<long long>(), p.cell_mask.as<int>(), p.base.as<int>(),
+                 p.level_on.as<unsigned char>(), ix.list_len, pl.lr, pl.seg.as<int2>(),
+                 pl.stats.as<long long>(), s);
   mark();
   kernels::round_lists(pl.r1, s);
   mark();

@@ -164,8 +164,9 @@ def algorithmic_bytes(stats, sp, meta, k):
     waves = sp["waves"]
     lists = (4 * stats[:, 2] + n1 * S + r1 * 2 * D + 4 * D + 4 * S + KO * 12).sum()
     pairs = len(stats) * meta["copies"]
-    # 16-byte table slots examined, plus the codes read and the segment written per (query, copy)
-    out = {"probe": int((stats[:, 1] * 16).sum() + pairs * (8 * len(meta["spacings"]) + 8)),
+    # the cell lookup happens inside the projection kernel: 16-byte table slots examined and the
+    # segment written per (query, copy), next to the fp16 queries read
+    out = {"project": int((stats[:, 1] * 16).sum() + pairs * 8 + len(stats) * 2 * D),
            "round_lists": int(lists)}
     if waves:
         rerank_w = stats[:, 7] - r1  # rows the waves read (ids already kept are not read again)

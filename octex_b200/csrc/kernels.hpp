@@ -53,15 +53,29 @@ struct project_tc_plan {
   alignas(64) unsigned char map_b[128];  // fp16 projections [copies * 32, ldu]
   int m = 0, copies = 0, ldu = 0;
 };
+/// The cell lookup done inside the projection's epilogue (table == nullptr: not done there; the
+/// codes are written out for the separate kernel instead). Needs level_on.
+struct cell_slot;
+struct tc_lookup {
+  const cell_slot* table = nullptr;
+  const long long* toff  = nullptr;
+  const int* tmask       = nullptr;
+  const int* base        = nullptr;
+  int list_len = 0, lr = 0;
+  int2* seg        = nullptr;  // [m, copies]
+  long long* stats = nullptr;  // [m, 8] += (levels tried, slots examined), may be null
+};
 /// True when the tensor-core kernel covers this index shape (4 blocks per copy).
 bool project_tc_supported(int blocks, int ldu);
 void project_tc_setup(project_tc_plan& p, const __half* qh, int m, const __half* ut, int copies, int ldu);
 /// codes [m, copies, L] (and Yout [m, copies * 32] fp16 when not null) from the operands of the
 /// plan. *error (device-visible int) becomes non-zero when a wait inside the kernel ran out.
 /// finest = the smallest spacing (host copy): coordinates small against it take the short decode.
+/// With look.table set, the lookup of the cells happens in the same kernel: seg is written, codes
+/// is not.
 void project_decode_tc(const project_tc_plan& p, int L, const __half* shift, const float* inv_f,
                        float finest, const unsigned char* level_on, long long* codes, __half* Yout,
-                       int* error, cudaStream_t s);
+                       const tc_lookup& look, int* error, cudaStream_t s);
 
 /// codes [n] = cell code of each row of y [n, 8*blocks] float32 scaled by inv_f.
 void cell_codes_f32(const float* y, int64_t n, int blocks, float inv_f, long long* codes,

@@ -142,6 +142,7 @@ __global__ void __launch_bounds__(kThreads, 2) project_decode_tc_kernel(
   const unsigned char* __restrict__ level_on,
   long long* __restrict__ codes,
   __half* __restrict__ Yout,
+  const tc_lookup look,
   int* __restrict__ error)
 {
   extern __shared__ unsigned char raw[];
@@ -257,12 +258,65 @@ __global__ void __launch_bounds__(kThreads, 2) project_decode_tc_kernel(
       for (int i = 0; i < 4; i++)
         dst[i] = *reinterpret_cast<const uint4*>(&yh[8 * i]);
     }
-    long long* out = codes + (static_cast<int64_t>(row) * Cg + c) * L;
-    for (int j = 0; j < L; j++) {
-      long long h = 0;
-      if (level_on == nullptr || level_on[c * L + j])
-        h = wild ? cell_code<4>(y, sm.inv_f[j]) : cell_code_tame<4>(y, sm.inv_f[j]);
-      out[j] = h;
+    if (look.table == nullptr) {
+      // codes of every level for a separate lookup kernel (and for inspection)
+      long long* out = codes + (static_cast<int64_t>(row) * Cg + c) * L;
+      for (int j = 0; j < L; j++) {
+        long long h = 0;
+        if (level_on == nullptr || level_on[c * L + j])
+          h = wild ? cell_code<4>(y, sm.inv_f[j]) : cell_code_tame<4>(y, sm.inv_f[j]);
+        out[j] = h;
+      }
+      continue;
+    }
+    // Lookup fused in (search_kernels.cuh:100-126: the finest level whose cell holds a list): the
+    // table slot of a level is requested as soon as its code is known and looked at after the next
+    // level has been decoded, so its latency hides behind that decode; once a level hits, the
+    // coarser ones are not decoded at all. No code goes to memory.
+    int2 sg         = make_int2(0, 0);
+    bool found      = false, pending = false;
+    int4 slot       = make_int4(0, 0, -1, 0);
+    long long slot_h = 0;
+    int slot_cl      = 0;
+    long long tried = 0, scanned = 0;
+    auto resolve = [&] {
+      tried++;
+      const unsigned mask = static_cast<unsigned>(look.tmask[slot_cl]);
+      const cell_slot* tb = look.table + look.toff[slot_cl];
+      unsigned s          = static_cast<unsigned>(slot_h) & mask;
+      for (unsigned probe = 0; probe <= mask; probe++) {
+        scanned++;
+        if (slot.z < 0) break;  // an empty slot ends the run: no such cell
+        const long long key = (static_cast<long long>(slot.y) << 32) | static_cast<unsigned>(slot.x);
+        if (key == slot_h) {
+          sg    = make_int2((look.base[slot_cl] + slot.z) * look.list_len, look.lr);
+          found = true;
+          break;
+        }
+        s    = (s + 1) & mask;
+        slot = __ldg(reinterpret_cast<const int4*>(tb + s));
+      }
+      pending = false;
+    };
+    for (int j = 0; j < L && !found; j++) {
+      const int cl = c * L + j;
+      if (!level_on[cl]) continue;
+      const long long h = wild ? cell_code<4>(y, sm.inv_f[j]) : cell_code_tame<4>(y, sm.inv_f[j]);
+      if (pending) resolve();
+      if (found) break;
+      slot_h  = h;
+      slot_cl = cl;
+      slot    = __ldg(reinterpret_cast<const int4*>(look.table + look.toff[cl] +
+                                                    (static_cast<unsigned>(h) & static_cast<unsigned>(look.tmask[cl]))));
+      pending = true;
+    }
+    if (pending && !found) resolve();
+    look.seg[static_cast<int64_t>(row) * Cg + c] = sg;
+    if (look.stats != nullptr) {
+      atomicAdd(reinterpret_cast<unsigned long long*>(look.stats + static_cast<int64_t>(row) * 8),
+                static_cast<unsigned long long>(tried));
+      atomicAdd(reinterpret_cast<unsigned long long*>(look.stats + static_cast<int64_t>(row) * 8 + 1),
+                static_cast<unsigned long long>(scanned));
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -328,7 +382,7 @@ void project_tc_setup(project_tc_plan& p, const __half* qh, int m, const __half*
 
 void project_decode_tc(const project_tc_plan& p, int L, const __half* shift, const float* inv_f,
                        float finest, const unsigned char* level_on, long long* codes, __half* Yout,
-                       int* error, cudaStream_t s)
+                       const tc_lookup& look, int* error, cudaStream_t s)
 {
   // |y| below this keeps |y / spacing| under the bound of the short decode at every level
   const float tame_y = finest > 0.f ? kTameLimit * finest * 0.99f : 0.f;
@@ -338,7 +392,7 @@ void project_decode_tc(const project_tc_plan& p, int L, const __half* shift, con
   std::memcpy(&b, p.map_b, sizeof(b));
   dim3 grid((p.copies * 32 + kTileN - 1) / kTileN, (p.m + kTileM - 1) / kTileM);
   project_decode_tc_kernel<<<grid, kThreads, sizeof(tc_smem) + 1024, s>>>(
-    a, b, p.m, p.copies, L, p.ldu / kTileK, shift, inv_f, tame_y, level_on, codes, Yout, error);
+    a, b, p.m, p.copies, L, p.ldu / kTileK, shift, inv_f, tame_y, level_on, codes, Yout, look, error);
 }
 
 }  // namespace octex_b200::kernels

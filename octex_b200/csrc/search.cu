@@ -133,13 +133,27 @@ void run_batch(index_impl const& ix, plan& pl, cudaStream_t s, std::vector<cudaE
                          pl.qh.as<__half>(), p.ldu, pl.qs.as<float>(), s);
   mark();
   const unsigned char* levels = pl.dbg.taps ? nullptr : p.level_on.as<unsigned char>();
+  // without inspection the cells are looked up where their codes are computed: no codes array, no
+  // lookup kernel
+  const bool fused_lookup = pl.use_tc && !pl.dbg.taps;
   if (pl.use_tc) {
     // tensor cores; the projected coordinates stay in TMEM unless they are asked for
     float finest = ix.spacings[0];
     for (float f : ix.spacings)
       finest = std::min(finest, f);
+    kernels::tc_lookup look;
+    if (fused_lookup) {
+      look.table    = p.cell_table.as<kernels::cell_slot>();
+      look.toff     = p.cell_off.as<long long>();
+      look.tmask    = p.cell_mask.as<int>();
+      look.base     = p.base.as<int>();
+      look.list_len = ix.list_len;
+      look.lr       = pl.lr;
+      look.seg      = pl.seg.as<int2>();
+      look.stats    = pl.stats.as<long long>();
+    }
     kernels::project_decode_tc(pl.tc, L, p.shift.as<__half>(), p.inv_f.as<float>(), finest, levels,
-                               pl.codes.as<long long>(), pl.dbg.taps ? pl.Y.as<__half>() : nullptr,
+                               pl.codes.as<long long>(), pl.dbg.taps ? pl.Y.as<__half>() : nullptr, look,
                                pl.tc_error_dev, s);
     mark();
   } else {
@@ -150,10 +164,11 @@ void run_batch(index_impl const& ix, plan& pl, cudaStream_t s, std::vector<cudaE
                           p.inv_f.as<float>(), levels, pl.codes.as<long long>(), s);
   }
   mark();
-  kernels::probe(pl.codes.as<long long>(), pl.m1, p.copies, L, p.cell_table.as<kernels::cell_slot>(),
-                 p.cell_off.as<long long>(), p.cell_mask.as<int>(), p.base.as<int>(),
-                 p.level_on.as<unsigned char>(), ix.list_len, pl.lr, pl.seg.as<int2>(),
-                 pl.stats.as<long long>(), s);
+  if (!fused_lookup)
+    kernels::probe(pl.codes.as<long long>(), pl.m1, p.copies, L, p.cell_table.as<kernels::cell_slot>(),
+                   p.cell_off.as<long long>(), p.cell_mask.as<int>(), p.base.as<int>(),
+                   p.level_on.as<unsigned char>(), ix.list_len, pl.lr, pl.seg.as<int2>(),
+                   pl.stats.as<long long>(), s);
   mark();
   kernels::round_lists(pl.r1, s);
   mark();

@@ -225,6 +225,11 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--copies", type=int, default=0, help="override the copies of the build")
     ap.add_argument("--search", default="", help="JSON search parameters (skips the ladder)")
+    ap.add_argument("--placement", default="replicate", choices=["replicate", "shard", "shard-rows"],
+                    help="with several GPUs: replicate = every GPU answers its own batches (weak "
+                         "scaling, no collective); shard = one batch, copies and the neighbor table "
+                         "split over the GPUs, kept lists exchanged over NCCL (strong scaling); "
+                         "shard-rows = shard with the sketch and the fp16 vectors dealt by rows too")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
@@ -246,8 +251,9 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     w = WORKLOADS[args.workload]
+    sharded = world > 1 and args.placement != "replicate"  # one batch answered by all GPUs together
     t0 = time.time()
-    base, queries = make_data(w, rank)
+    base, queries = make_data(w, 0 if sharded else rank)
     log(f"[rank {rank}] data {time.time() - t0:.1f}s")
     t0 = time.time()
     arrays, meta = build_index.build_arrays(base, build_index.IndexParams(**w["build"]),
@@ -255,7 +261,14 @@ def main():
                                             verbose=(rank == 0))
     torch.cuda.synchronize()
     log(f"[rank {rank}] index built in {time.time() - t0:.1f}s")
-    idx = octex_b200.attach(arrays, meta, borrow=True)
+    if sharded:
+        from octex_b200 import dist as odist
+        rows = args.placement == "shard-rows"
+        idx = octex_b200.attach(arrays, meta, borrow=False, rank=rank, world=world, placement="shard",
+                                shard_vectors=rows, sketch="shard" if rows else "replicate")
+        odist.connect(idx)
+    else:
+        idx = octex_b200.attach(arrays, meta, borrow=True)
     index_bytes = sum(v.numel() * v.element_size() for v in arrays.values())
     nq = len(queries)
     q_dev = torch.as_tensor(queries, device="cuda")
@@ -355,18 +368,23 @@ def main():
             dist.destroy_process_group()
         return
 
-    qps = world * nq * args.steps / (total_ms * 1e-3)
-    e2e_qps = world * nq * args.steps / (e2e_ms * 1e-3)
+    batches = 1 if sharded else world  # batches answered per step over all GPUs
+    qps = batches * nq * args.steps / (total_ms * 1e-3)
+    e2e_qps = batches * nq * args.steps / (e2e_ms * 1e-3)
     peaks = {}
     try:
         peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
     except OSError:
         pass
     peak = float(peaks.get("hbm_gbs", 6650.0))
-    timed = {k_: v for k_, v in kernel_ms.items() if k_ in alg}
+    # sharded: the counters of this GPU's waves cover its slice of the batch only and the wave's time
+    # includes the exchange, so the roofline is taken over the first-round kernels
+    timed = {k_: v for k_, v in kernel_ms.items()
+             if k_ in alg and not (sharded and k_ == "round_rows")}
     top = max(timed, key=lambda k_: timed[k_] * launches_per_step.get(k_, 1))
     achieved = alg[top] / (kernel_ms[top] * 1e-3) / 1e9
-    captured = (args.workload == "descriptor-1m" and not args.copies and sp == LADDER[0])
+    captured = (args.workload == "descriptor-1m" and not args.copies and sp == LADDER[0]
+                and not sharded)
     roofline = {"bound": "hbm", "kernel": top, "achieved": achieved, "peak": peak, "unit": "GB/s",
                 "frac": achieved / peak, "traffic": NCU_TRAFFIC.get(top) if captured else None,
                 "peak_source": "MEASURED_PEAKS.json" if peaks else "fallback 6650 GB/s",
@@ -377,9 +395,10 @@ def main():
     line = {
         "metric": METRIC, "value": qps, "unit": "queries/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f16/f32/i8", "data": "synthetic",
+        "scaling": "strong" if sharded else "weak", "vs_baseline": None, "dtype": "f16/f32/i8",
+        "data": "synthetic",
         "config": {"workload": args.workload, "n": w["n"], "dim": w["dim"], "queries_per_step": nq,
-                   "k": K, "placement": "replicate", "build": w["build"], "search": sp,
+                   "k": K, "placement": args.placement if world > 1 else "one GPU", "build": w["build"], "search": sp,
                    "recall_at_10": rec, "recall_at_10_e2e": rec_e2e,
                    "index_bytes": index_bytes, "l2": "flushed between timed steps (256 MB fill)",
                    "mean_per_query": {"levels_tried": float(stats[:, 0].mean()),

@@ -245,20 +245,32 @@ __device__ __forceinline__ radix_cut_t radix_cut(HiAt hi_at, LoAt lo_at, int n, 
                      (static_cast<unsigned long long>(mask_hi) << 32) | mask_lo};
 }
 
+/// float(h) - q for an fp16 bit pattern h: the mixed-precision subtract of sm_100 (PTX ISA 8.6),
+/// the same value as converting first (the conversion is exact) without the conversion.
+__device__ __forceinline__ float half_minus(unsigned short h, float q)
+{
+  float d;
+  asm("sub.rn.f32.f16 %0, %1, %2;" : "=f"(d) : "h"(h), "f"(q));
+  return d;
+}
+
 /// Eight int8 codes (two 32-bit words) against eight (scale, query) pairs: sum of
 /// (code * scale - q)^2 with two fused multiply-adds per code, in code order. The int8 -> float
-/// conversion goes through the mantissa of 2^23 (exact for every int8 value), which keeps it off
-/// the conversion pipe.
+/// conversion: one byte permute makes the fp16 patterns 0x64bb = 1024 + (code + 128) of two codes,
+/// and the mixed-precision subtract of 1152 gives each code exactly, off the conversion pipe.
 __device__ __forceinline__ float sketch_chunk8(uint2 w, const float* s, const float* q)
 {
   const unsigned x0 = w.x ^ 0x80808080u, x1 = w.y ^ 0x80808080u;  // code + 128 in every byte
   float d           = 0.f;
 #pragma unroll
-  for (int b = 0; b < 8; b++) {
-    const float code =
-      __fadd_rn(__uint_as_float(__byte_perm(b < 4 ? x0 : x1, 0x4B000000u, 0x7650 + (b & 3))), -8388736.0f);
-    const float t = __fmaf_rn(code, s[b], -q[b]);
-    d             = __fmaf_rn(t, t, d);
+  for (int p = 0; p < 4; p++) {
+    const unsigned hh = __byte_perm(p < 2 ? x0 : x1, 0x64646464u, (p & 1) ? 0x4342 : 0x4140);
+    const float c0    = half_minus(static_cast<unsigned short>(hh & 0xffffu), 1152.0f);
+    const float c1    = half_minus(static_cast<unsigned short>(hh >> 16), 1152.0f);
+    const float t0    = __fmaf_rn(c0, s[2 * p], -q[2 * p]);
+    d                 = __fmaf_rn(t0, t0, d);
+    const float t1    = __fmaf_rn(c1, s[2 * p + 1], -q[2 * p + 1]);
+    d                 = __fmaf_rn(t1, t1, d);
   }
   return d;
 }
@@ -364,13 +376,12 @@ __device__ __forceinline__ void exact_pair(const uint4* const (&row)[2], int Drt
         const float qq[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
 #pragma unroll
         for (int u = 0; u < 2; u++) {
-          const __half2* h2 = reinterpret_cast<const __half2*>(&v[s][u]);
+          const unsigned h2[4] = {v[s][u].x, v[s][u].y, v[s][u].z, v[s][u].w};
 #pragma unroll
           for (int t = 0; t < 4; t++) {
-            const float2 x = __half22float2(h2[t]);
-            const float a  = __fsub_rn(x.x, qq[2 * t]);
-            const float b  = __fsub_rn(x.y, qq[2 * t + 1]);
-            acc[u][t]      = __fmaf_rn(b, b, __fmaf_rn(a, a, acc[u][t]));
+            const float a = half_minus(static_cast<unsigned short>(h2[t] & 0xffffu), qq[2 * t]);
+            const float b = half_minus(static_cast<unsigned short>(h2[t] >> 16), qq[2 * t + 1]);
+            acc[u][t]     = __fmaf_rn(b, b, __fmaf_rn(a, a, acc[u][t]));
           }
         }
       }

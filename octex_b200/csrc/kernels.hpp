@@ -14,7 +14,7 @@ constexpr int kMaxRerank   = 512;    // exact rerank depth per round
 constexpr int kMaxKeepSort = 1024;   // kept + reranked keys sorted together (exact ranking)
 constexpr int kMaxSketchKO = 1024;   // kept entries when ranking by sketch
 constexpr int kMaxExpanded = 6144;   // start points expanded by earlier waves
-constexpr int kRoundThreads = 128;
+constexpr int kRoundThreads = 128;  // threads of a query block unless its shared memory asks for more
 
 /// Slots of the hash set that collects `total` entries: twelfths / 12 slots per entry (24 = half
 /// full at most, 16 = three quarters), a multiple of four, between kMinHash and cap. (The reference,
@@ -150,6 +150,8 @@ struct round_args {
   int ht_slots = 0;   // ints of the hash set region (>= largest set used, >= pick_slots)
   int cap_slots = 0;  // largest gather hash set (slots)
   int hash_twelfths = 16;  // slots per 12 gathered entries (host: as sparse as shared memory allows)
+  int threads = kRoundThreads;  // threads per query block: 128, 256 or 512 (host: the smallest
+                                // that still fills a multiprocessor with the blocks that fit it)
   int nmax = 0;       // capacity of the candidate / distance arrays
   int P = 0;          // keys sorted by the merge (power of two >= KO)
   int* cand_global = nullptr;    // [m, nmax] when the candidates do not fit shared memory

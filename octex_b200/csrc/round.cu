@@ -57,7 +57,7 @@ struct round_layout {
     st     = take(a.nseg);
     len    = take(a.nseg);
     hist   = take(256);
-    wsum   = take(16);
+    wsum   = take(20);
     ctrl   = take(8);
     kid    = take(a.KO);
     kd     = take(a.KO);
@@ -71,11 +71,13 @@ __device__ __forceinline__ unsigned home_slot(int id, int slots)
   return __umulhi(static_cast<unsigned>(id) * kIdHash, static_cast<unsigned>(slots));
 }
 
-/// Exclusive prefix of v over the block (kRoundThreads threads); total = the sum.
+/// Exclusive prefix of v over the block (kThreads threads); total = the sum. wsum: kThreads / 32 + 1
+/// words.
+template <int kThreads = kRoundThreads>
 __device__ __forceinline__ int block_scan(int v, int* wsum, int& total)
 {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  constexpr int nw = kRoundThreads / 32;
+  constexpr int nw = kThreads / 32;
   int inc          = v;
 #pragma unroll
   for (int o = 1; o < 32; o <<= 1) {
@@ -550,8 +552,11 @@ __device__ __forceinline__ void merge_into_kept(unsigned long long* pool,
 }
 
 
-template <bool kRows, bool kDealt>
-__global__ void __launch_bounds__(kRoundThreads, 8) round_kernel(const round_args a)
+// kThreads: 128 with eight blocks per multiprocessor when a block's shared memory allows that; a
+// round whose hash set is too large for eight blocks runs 256 or 512 threads per block instead, so
+// that the blocks that do fit still bring 32 warps to a multiprocessor.
+template <bool kRows, bool kDealt, int kThreads>
+__global__ void __launch_bounds__(kThreads, 1024 / kThreads) round_kernel(const round_args a)
 {
   extern __shared__ __align__(16) int smem[];
   const round_layout lay(a);
@@ -626,7 +631,7 @@ __global__ void __launch_bounds__(kRoundThreads, 8) round_kernel(const round_arg
       }
     }
     __syncthreads();
-    const int per       = (a.KO + kRoundThreads - 1) / kRoundThreads;
+    const int per       = (a.KO + kThreads - 1) / kThreads;
     const int i0        = threadIdx.x * per;
     unsigned fresh_bits = 0;
     int mine            = 0;
@@ -651,7 +656,7 @@ __global__ void __launch_bounds__(kRoundThreads, 8) round_kernel(const round_arg
       }
     }
     int nfresh = 0;
-    int at     = block_scan(mine, wsum, nfresh);
+    int at     = block_scan<kThreads>(mine, wsum, nfresh);
     for (int i = i0; i < min(a.KO, i0 + per); i++)
       if (fresh_bits & (1u << (i - i0))) {
         if (at < a.nseg) {
@@ -687,7 +692,7 @@ __global__ void __launch_bounds__(kRoundThreads, 8) round_kernel(const round_arg
         asm volatile("prefetch.global.L2 [%0];" ::"l"(run + sl.y * 4 - 4));
       }
     }
-    block_scan(mine, wsum, total);
+    block_scan<kThreads>(mine, wsum, total);
   }
 
   // distinct ids through an open-addressing hash set (search_kernels.cuh:191-225); a group of lps
@@ -701,10 +706,10 @@ __global__ void __launch_bounds__(kRoundThreads, 8) round_kernel(const round_arg
   {
     const int maxlen = kRows ? a.table_len : a.lr;
     int lps          = 1;
-    while (lps < maxlen && lps < kRoundThreads)
+    while (lps < maxlen && lps < kThreads)
       lps <<= 1;
     const int within0 = threadIdx.x & (lps - 1);
-    const int spp     = kRoundThreads / lps;  // segments per pass
+    const int spp     = kThreads / lps;  // segments per pass
     const int seg0    = threadIdx.x / lps;
     // loop bounds are the same for every thread: the slot counter below is updated once per warp
     for (int wb = 0; wb < maxlen; wb += lps) {
@@ -926,7 +931,7 @@ __global__ void __launch_bounds__(kRoundThreads, 8) round_kernel(const round_arg
       int mine = 0;
       for (int i = threadIdx.x; i < ns; i += blockDim.x)
         mine += sid[i] >= 0;
-      block_scan(mine, wsum, reranked);
+      block_scan<kThreads>(mine, wsum, reranked);
     }
     tick(4);
     exact_distances<kDealt>(sid, ns, a.vectors, a.vector_map, a.D, fq, sdv);
@@ -1052,38 +1057,60 @@ __global__ void merge_kept_kernel(const long long* __restrict__ src_i,
 
 size_t round_smem_bytes(const round_args& a) { return sizeof(int) * round_layout(a).words; }
 
-void round_allow_smem(size_t bytes)
-{
-  const int b = static_cast<int>(bytes);
-  cudaFuncSetAttribute(round_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, b);
-  cudaFuncSetAttribute(round_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, b);
-  cudaFuncSetAttribute(round_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, b);
-  cudaFuncSetAttribute(round_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, b);
-}
-
 namespace {
+template <bool kRows, bool kDealt, int kThreads>
+void launch_round(const round_args& a, cudaStream_t s)
+{
+  round_kernel<kRows, kDealt, kThreads><<<a.m, kThreads, round_smem_bytes(a), s>>>(a);
+}
+template <bool kRows, bool kDealt>
+void launch_round(const round_args& a, cudaStream_t s)
+{
+  if (a.threads >= 512)
+    launch_round<kRows, kDealt, 512>(a, s);
+  else if (a.threads >= 256)
+    launch_round<kRows, kDealt, 256>(a, s);
+  else
+    launch_round<kRows, kDealt, 128>(a, s);
+}
+template <bool kRows, bool kDealt>
+void allow_smem(int b)
+{
+  cudaFuncSetAttribute(round_kernel<kRows, kDealt, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, b);
+  cudaFuncSetAttribute(round_kernel<kRows, kDealt, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, b);
+  cudaFuncSetAttribute(round_kernel<kRows, kDealt, 512>, cudaFuncAttributeMaxDynamicSharedMemorySize, b);
+}
 bool dealt(const round_args& a)
 {
   return a.table_map.ptrs != nullptr || a.sketch_map.ptrs != nullptr || a.vector_map.ptrs != nullptr;
 }
 }  // namespace
 
+void round_allow_smem(size_t bytes)
+{
+  const int b = static_cast<int>(bytes);
+  allow_smem<false, false>(b);
+  allow_smem<true, false>(b);
+  allow_smem<false, true>(b);
+  allow_smem<true, true>(b);
+}
+
 void round_lists(const round_args& a, cudaStream_t s)
 {
   if (a.m <= 0) return;
   if (dealt(a))
-    round_kernel<false, true><<<a.m, kRoundThreads, round_smem_bytes(a), s>>>(a);
+    launch_round<false, true>(a, s);
   else
-    round_kernel<false, false><<<a.m, kRoundThreads, round_smem_bytes(a), s>>>(a);
+    launch_round<false, false>(a, s);
 }
 
 void round_rows(const round_args& a, cudaStream_t s)
 {
   if (a.m <= 0) return;
   if (dealt(a))
-    round_kernel<true, true><<<a.m, kRoundThreads, round_smem_bytes(a), s>>>(a);
+    launch_round<true, true>(a, s);
   else
-    round_kernel<true, false><<<a.m, kRoundThreads, round_smem_bytes(a), s>>>(a);
+    launch_round<true, false>(a, s);
 }
 
 void final_rerank(const long long* si, int KO, int R, const __half* vectors, row_map vector_map, int D,

@@ -84,6 +84,11 @@ void size_round(plan& pl, kernels::round_args& r, int entries_max, int pick_entr
     r.dist_global = pl.scratch_dist.back().as<float>();
   }
   pl.smem_max = std::max(pl.smem_max, kernels::round_smem_bytes(r));
+  // threads per block: a multiprocessor runs 1024 threads of this kernel (64 registers each); when
+  // fewer than eight blocks fit its shared memory, the blocks get more threads to make up for it
+  const size_t per_block = kernels::round_smem_bytes(r) + 1024;
+  const int fit          = static_cast<int>(std::max<size_t>((size_t{228} << 10) / per_block, 1));
+  r.threads              = fit >= 8 ? 128 : fit >= 4 ? 256 : 512;
 }
 
 }  // namespace

@@ -149,7 +149,9 @@ def test_stages_bit_exact(oracle, gpu_small):
     dict(read=8, starts=64, waves=2, sketch_rank=True, final_rerank=32),
     dict(read=8, starts=64, waves=2, sketch_rank=True, final_rerank=0),
     dict(read=8, starts=600, waves=1, sketch_rank=True, final_rerank=64),
-    dict(read=64, starts=512, waves=2, rerank=512, wave_rerank=512),
+    dict(read=64, starts=512, waves=2, rerank=512, wave_rerank=512),  # 512-thread query blocks
+    dict(read=16, starts=128, waves=2, rerank=256, wave_rerank=256),  # 256-thread query blocks
+    dict(read=32, starts=256, waves=1, rerank=384, wave_rerank=512),
 ])
 def test_results_identical(oracle, gpu_small, gpu_wide, kw):
     for idx, arrays, meta, _, queries in (gpu_small, gpu_wide):

@@ -6,6 +6,8 @@ One process per GPU (torchrun for N > 1).  A step is one search of one 10 000-qu
 N = 1 the workload is "descriptor-1m" (1 000 000 x 128 descriptor-like rows, replicate placement);
 with N > 1 every rank holds the whole index and answers its own 10 000-query batch (weak scaling,
 no data-path collective), as the reference's replicate placement slices queries over GPUs.
+`--placement shard` (N > 1) answers ONE batch per step with the copies and the neighbor table split
+over the GPUs and the kept lists exchanged over NCCL (strong scaling).
 Data are seeded synthetic stand-ins for the public sets the reference is quoted on.
 
 Rank 0 prints one JSON line.  `value` is measured with the queries already on the GPU (the
@@ -40,6 +42,11 @@ WORKLOADS = {
         gen="descriptor_like", n=1_000_000, dim=128, nq=10_000,
         build=dict(copies=64, blocks=4, pca_dims=64, list_len=32, min_cell=16, log_buckets=20,
                    sketch_width=64, table_len=64)),
+    # the generator of the 10M / 1B embedding configurations at a size one GPU builds in seconds
+    "embedding-1m": dict(
+        gen="embedding_like", n=1_000_000, dim=96, nq=10_000,
+        build=dict(copies=64, blocks=4, pca_dims=64, list_len=32, min_cell=16, log_buckets=20,
+                   sketch_width=64, table_len=64)),
     "plumbing-100k": dict(
         gen="plumbing", n=100_000, dim=128, nq=1_000,
         build=dict(copies=32, blocks=4, pca_dims=64, list_len=32, min_cell=1, log_buckets=16,
@@ -53,6 +60,8 @@ LADDER = [
     dict(read=32, starts=32, waves=3, rerank=256, wave_rerank=256),
     dict(read=32, starts=128, waves=3, rerank=256, wave_rerank=256),
     dict(read=32, starts=128, waves=2, rerank=512, wave_rerank=512),
+    dict(read=32, starts=192, waves=3, rerank=384, wave_rerank=384),
+    dict(read=32, starts=256, waves=3, rerank=512, wave_rerank=512),
     dict(read=32, starts=256, waves=4, rerank=512, wave_rerank=512),
 ]
 
@@ -249,6 +258,9 @@ def main():
     assert torch.cuda.is_available(), "bench.py needs a GPU (there is no CPU path)"
     torch.cuda.set_device(local)
     if world > 1:
+        # NCCL's own log lines (its version banner among them) go to stderr: stdout carries the one
+        # JSON line
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     w = WORKLOADS[args.workload]
     sharded = world > 1 and args.placement != "replicate"  # one batch answered by all GPUs together

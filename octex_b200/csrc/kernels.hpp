@@ -155,7 +155,7 @@ struct round_args {
   int nmax = 0;       // capacity of the candidate / distance arrays
   int P = 0;          // keys sorted by the merge (power of two >= KO)
   int* cand_global = nullptr;    // [m, nmax] when the candidates do not fit shared memory
-  float* dist_global = nullptr;  // [m, nmax]
+  float* dist_global = nullptr;  // [m, nmax] when the region of the hash set (ht_slots) cannot hold them
   // rows dealt over GPUs (all empty: every array is whole behind its pointer)
   row_map table_map, sketch_map, vector_map;
   // observation (all may be null)

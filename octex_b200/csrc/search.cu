@@ -79,9 +79,14 @@ void size_round(plan& pl, kernels::round_args& r, int entries_max, int pick_entr
     OCTEX_EXPECTS(kernels::round_smem_bytes(r) <= kSmemHardLimit,
                   "octex: the round does not fit shared memory");
     pl.scratch_cand.push_back(alloc<int>(pl, device, int64_t{r.m} * r.nmax));
-    pl.scratch_dist.push_back(alloc<float>(pl, device, int64_t{r.m} * r.nmax));
     r.cand_global = pl.scratch_cand.back().as<int>();
-    r.dist_global = pl.scratch_dist.back().as<float>();
+    // the sketch distances still go where the hash set was when that region holds them all (the
+    // selection makes several passes over them)
+    r.dist_global = nullptr;
+    if (r.ht_slots < r.nmax) {
+      pl.scratch_dist.push_back(alloc<float>(pl, device, int64_t{r.m} * r.nmax));
+      r.dist_global = pl.scratch_dist.back().as<float>();
+    }
   }
   pl.smem_max = std::max(pl.smem_max, kernels::round_smem_bytes(r));
   // threads per block: a multiprocessor runs 1024 threads of this kernel (64 registers each); when

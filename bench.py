@@ -234,6 +234,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--copies", type=int, default=0, help="override the copies of the build")
     ap.add_argument("--search", default="", help="JSON search parameters (skips the ladder)")
+    ap.add_argument("--queries", type=int, default=0,
+                    help="queries per batch instead of the workload's (small profiler captures)")
     ap.add_argument("--placement", default="replicate", choices=["replicate", "shard", "shard-rows"],
                     help="with several GPUs: replicate = every GPU answers its own batches (weak "
                          "scaling, no collective); shard = one batch, copies and the neighbor table "
@@ -246,6 +248,8 @@ def main():
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if args.copies:
         WORKLOADS[args.workload]["build"]["copies"] = args.copies
+    if args.queries:
+        WORKLOADS[args.workload]["nq"] = args.queries
     if args.impl == "reference":
         run_reference(args, rank, world)
         return
@@ -396,7 +400,7 @@ def main():
     top = max(timed, key=lambda k_: timed[k_] * launches_per_step.get(k_, 1))
     achieved = alg[top] / (kernel_ms[top] * 1e-3) / 1e9
     captured = (args.workload == "descriptor-1m" and not args.copies and sp == LADDER[0]
-                and not sharded)
+                and not sharded and not args.queries)
     roofline = {"bound": "hbm", "kernel": top, "achieved": achieved, "peak": peak, "unit": "GB/s",
                 "frac": achieved / peak, "traffic": NCU_TRAFFIC.get(top) if captured else None,
                 "peak_source": "MEASURED_PEAKS.json" if peaks else "fallback 6650 GB/s",

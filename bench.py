@@ -219,7 +219,30 @@ def run_reference(args, rank, world):
             "cpu_baseline": {"value": qps, "unit": "queries/s", "cores": cores, "kind": "port",
                              "sample": f"{len(sample)} of {w['nq']} queries per step, same index"},
             "e2e": {"value": qps, "unit": "queries/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-    print(json.dumps(line), flush=True)
+    emit(line)
+
+
+# stdout carries exactly one line, the JSON: libraries that log there (NCCL prints its version banner
+# on stdout whatever its log file is) are sent to stderr by pointing descriptor 1 at descriptor 2
+# for the run, and the line is written to the saved descriptor
+_STDOUT_FD = None
+
+
+def claim_stdout():
+    global _STDOUT_FD
+    if _STDOUT_FD is None:
+        sys.stdout.flush()
+        _STDOUT_FD = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit(line):
+    data = (json.dumps(line) + "\n").encode()
+    if _STDOUT_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_STDOUT_FD, data)
 
 
 def main():
@@ -242,6 +265,7 @@ def main():
                          "split over the GPUs, kept lists exchanged over NCCL (strong scaling); "
                          "shard-rows = shard with the sketch and the fp16 vectors dealt by rows too")
     args = ap.parse_args()
+    claim_stdout()
     args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -262,9 +286,6 @@ def main():
     assert torch.cuda.is_available(), "bench.py needs a GPU (there is no CPU path)"
     torch.cuda.set_device(local)
     if world > 1:
-        # NCCL's own log lines (its version banner among them) go to stderr: stdout carries the one
-        # JSON line
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     w = WORKLOADS[args.workload]
     sharded = world > 1 and args.placement != "replicate"  # one batch answered by all GPUs together
@@ -436,7 +457,7 @@ def main():
             line["cpu_baseline"] = cpu_baseline(arrays, meta, queries, sp, args)
         except Exception as e:  # the baseline is a report, never a reason to lose the GPU numbers
             line["cpu_baseline"] = {"value": None, "error": str(e)}
-    print(json.dumps(line), flush=True)
+    emit(line)
     if world > 1:
         dist.destroy_process_group()
 

@@ -452,7 +452,7 @@ def main():
         "wall_s_timed_region": wall,
         "roofline": roofline,
     }
-    if not args.no_cpu_baseline:
+    if not args.no_cpu_baseline and world == 1:  # the CPU leg is timed once, beside the one-GPU run
         try:
             line["cpu_baseline"] = cpu_baseline(arrays, meta, queries, sp, args)
         except Exception as e:  # the baseline is a report, never a reason to lose the GPU numbers

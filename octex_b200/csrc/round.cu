@@ -344,6 +344,49 @@ __device__ __forceinline__ void sketch_rows(const int* cand, int n, const signed
   }
 }
 
+/// As sketch_rows for a sketch of exactly 16 * kLw codes, a lane scoring two neighbouring 8-code
+/// chunks of a row (one 16-byte load): the two chunk sums are added in the lane (the butterfly's
+/// stride-1 step), strides 2, 4, ... follow over the kLw lanes of the row — the same sum, bit for
+/// bit. Half the lanes per row means half the addressing and butterfly work per row; measured, a
+/// wave gains 1.5-4 % from it and the first round loses 1-3 %, so only the waves use it.
+template <int kLw, bool kDealt>
+__device__ __forceinline__ void sketch_rows16(const int* cand, int n, const signed char* __restrict__ sketch,
+                                              const row_map& map, const float* sc, const float* qv,
+                                              float* dist)
+{
+  constexpr int kG = 32 / kLw;  // rows per warp and step
+  constexpr int S  = 16 * kLw;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int sub = lane % kLw, grp = lane / kLw;
+  float cs[16], cq[16];
+#pragma unroll
+  for (int b = 0; b < 16; b++) {
+    cs[b] = sc[sub * 16 + b];
+    cq[b] = qv[sub * 16 + b];
+  }
+  const int rpp = nw * kG;  // rows per step of the block
+  for (int jb = 0; jb < n; jb += 2 * rpp) {
+    uint4 w[2];
+    int j[2];
+#pragma unroll
+    for (int u = 0; u < 2; u++) {
+      j[u]         = jb + u * rpp + warp * kG + grp;
+      const int id = cand[min(j[u], n - 1)];
+      w[u] = __ldg(reinterpret_cast<const uint4*>(row_of<kDealt>(sketch, map, id, S)) + sub);
+    }
+#pragma unroll
+    for (int u = 0; u < 2; u++) {
+      const float d0 = sketch_chunk8(make_uint2(w[u].x, w[u].y), cs, cq);
+      const float d1 = sketch_chunk8(make_uint2(w[u].z, w[u].w), cs + 8, cq + 8);
+      float d        = __fadd_rn(d0, d1);
+#pragma unroll
+      for (int o = 1; o < kLw; o <<= 1)
+        d = __fadd_rn(d, __shfl_xor_sync(0xffffffffu, d, o));
+      if (j[u] < n && sub == 0) dist[j[u]] = d;
+    }
+  }
+}
+
 /// Rows j and j + stride of a lane group: squared distances of two fp16 rows to the query fq
 /// (shared memory, read 16 bytes at a time).
 /// Both row pointers are valid (a row that is not wanted is replaced by any row by the caller, who
@@ -780,7 +823,11 @@ __global__ void __launch_bounds__(kThreads, 1024 / kThreads) round_kernel(const 
   // query coordinates in registers, the chunks of a row summed by a butterfly over its lanes
   // (strides 1, 2, 4, ...); four rows per lane group in flight. A sketch wider than 256 gives a
   // lane a second chunk (c + 32), added last.
-  if (S == 64) {
+  if (kRows && S == 64) {
+    sketch_rows16<4, kDealt>(cand, n, a.sketch, a.sketch_map, sc, qv, dist);
+  } else if (kRows && S == 128) {
+    sketch_rows16<8, kDealt>(cand, n, a.sketch, a.sketch_map, sc, qv, dist);
+  } else if (S == 64) {
     sketch_rows<8, kDealt, true>(cand, n, a.sketch, a.sketch_map, S, sc, qv, dist);
   } else if (S == 128) {
     sketch_rows<16, kDealt, true>(cand, n, a.sketch, a.sketch_map, S, sc, qv, dist);

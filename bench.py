@@ -2,12 +2,15 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload NAME]
 
-One process per GPU (torchrun for N > 1).  A step is one search of one 10 000-query batch.  At
-N = 1 the workload is "descriptor-1m" (1 000 000 x 128 descriptor-like rows, replicate placement);
-with N > 1 every rank holds the whole index and answers its own 10 000-query batch (weak scaling,
-no data-path collective), as the reference's replicate placement slices queries over GPUs.
-`--placement shard` (N > 1) answers ONE batch per step with the copies and the neighbor table split
-over the GPUs and the kept lists exchanged over NCCL (strong scaling).
+One process per GPU (torchrun for N > 1).  A step is one search of ONE 10 000-query batch of the
+workload "descriptor-1m" (1 000 000 x 128 descriptor-like rows).  With one GPU the whole index is on
+it.  With N > 1 the index is placed with `placement = shard`: the copies and the rows of the
+neighbor table are split over the GPUs, every GPU runs the first round of all queries over its
+copies, the kept lists are exchanged over NCCL, every GPU runs the waves of its slice of the batch
+and the results are gathered — the same batch answered by all GPUs together, so the work per step
+is fixed as N grows ("scaling": "strong").  The same run also reports, as secondary fields, the
+throughput of N independent whole-index replicas each answering its own batches (`replicas_qps`,
+no collective) and how the sharded answer compares with one GPU's and with the CPU checker's.
 Data are seeded synthetic stand-ins for the public sets the reference is quoted on.
 
 Rank 0 prints one JSON line.  `value` is measured with the queries already on the GPU (the
@@ -84,27 +87,73 @@ def log(*a):
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
+    """SM clock and throttle reasons of one GPU, sampled every few milliseconds from before the
+    warm-up until after the timed region (read-only NVML queries; `nvidia-smi` in a loop where the
+    NVML binding is missing); `summary` reports the samples that fall inside the timed region."""
+    REASONS = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20),
+               ("sw_power_cap", 0x4))
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, gpu):
-        self.gpu, self.rows, self.proc = gpu, [], None
+    def __init__(self, gpu, uuid=None, period_s=0.002):
+        self.gpu, self.uuid, self.period = gpu, uuid, period_s
+        self.rows, self.proc, self.thread = [], None, None
         self.t0 = self.t1 = None
+        self.stop = threading.Event()
+        self.max_mhz = None
+        self.how = None
+
+    def _nvml_loop(self, nv, handle):
+        while not self.stop.is_set():
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(handle, nv.NVML_CLOCK_SM)
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(handle)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(handle)
+                self.rows.append((time.perf_counter(), float(mhz), int(mask)))
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def _smi_loop(self):
+        for line in self.proc.stdout:
+            c = [x.strip() for x in line.split(",")]
+            if len(c) >= 6 and c[0].replace(".", "").isdigit():
+                mask = sum(bit for (_, bit), v in zip(self.REASONS, c[2:6]) if v.lower().startswith("active"))
+                self.max_mhz = float(c[1]) if c[1].replace(".", "").isdigit() else self.max_mhz
+                self.rows.append((time.perf_counter(), float(c[0]), mask))
 
     def __enter__(self):
-        """Starts sampling (before the warm-up, so that samples are already arriving when the timed
-        region begins); ``begin`` / ``end`` bracket the timed region."""
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", str(self.gpu), f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "20"],
-                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
+            import pynvml as nv
+            nv.nvmlInit()
+            handle = None
+            if self.uuid:
+                for cand in (self.uuid, "GPU-" + self.uuid):
+                    try:
+                        handle = nv.nvmlDeviceGetHandleByUUID(cand.encode() if isinstance(cand, str) else cand)
+                        break
+                    except Exception:
+                        handle = None
+            if handle is None:
+                handle = nv.nvmlDeviceGetHandleByIndex(self.gpu)
+            self.max_mhz = float(nv.nvmlDeviceGetMaxClockInfo(handle, nv.NVML_CLOCK_SM))
+            self.thread = threading.Thread(target=self._nvml_loop, args=(nv, handle), daemon=True)
+            self.how = "nvml"
+        except Exception:
+            try:
+                self.proc = subprocess.Popen(
+                    ["nvidia-smi", "-i", str(self.gpu), f"--query-gpu={self.FIELDS}",
+                     "--format=csv,noheader,nounits", "-lms", "5"],
+                    stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                self.thread = threading.Thread(target=self._smi_loop, daemon=True)
+                self.how = "nvidia-smi"
+            except OSError:
+                self.thread = None
+        if self.thread is not None:
             self.thread.start()
-        except OSError:
-            self.proc = None
         return self
 
     def begin(self):
@@ -113,29 +162,31 @@ class ClockSampler:
     def end(self):
         self.t1 = time.perf_counter()
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.rows.append((time.perf_counter(), [c.strip() for c in line.split(",")]))
-
     def __exit__(self, *exc):
+        time.sleep(0.02)
+        self.stop.set()
         if self.proc is not None:
-            time.sleep(0.05)
             self.proc.terminate()
             self.proc.wait(timeout=5)
+        if self.thread is not None:
+            self.thread.join(timeout=2)
 
     def summary(self):
-        rows = [r for t, r in self.rows
-                if self.t0 is not None and self.t0 <= t <= (self.t1 or t) + 0.03]
-        if not rows:  # a region shorter than the sampling period: the samples nearest to it
-            rows = [r for _, r in self.rows[-3:]]
-        sm = [float(r[0]) for r in rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
-        mx = [float(r[1]) for r in rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
-        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        reasons = [n for i, n in enumerate(names)
-                   if any(len(r) >= 6 and r[2 + i].lower().startswith("active") for r in rows)]
-        return {"sm_mhz": statistics.median(sm) if sm else None,
-                "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
-                "samples": len(sm)}
+        inside = [r for r in self.rows if self.t0 is not None and self.t0 <= r[0] <= (self.t1 or r[0])]
+        near = False
+        if not inside and self.rows and self.t0 is not None:
+            # no sample fell inside: the ones nearest to the region on either side
+            mid = 0.5 * (self.t0 + (self.t1 or self.t0))
+            inside = sorted(self.rows, key=lambda r: abs(r[0] - mid))[:4]
+            near = True
+        sm = [r[1] for r in inside]
+        mask = 0
+        for r in inside:
+            mask |= r[2]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": self.max_mhz,
+                "reasons": [n for n, bit in self.REASONS if mask & bit],
+                "samples": len(sm), "samples_total": len(self.rows), "source": self.how,
+                "nearest_to_region": near}
 
 
 def make_data(w, rank_seed):
@@ -185,6 +236,12 @@ def algorithmic_bytes(stats, sp, meta, k):
     return out
 
 
+def workload_config(args, w, sp, world):
+    """The part of `config` that names the workload; both arms print the same."""
+    return {"workload": args.workload, "n": w["n"], "dim": w["dim"], "queries_per_step": w["nq"],
+            "k": K, "placement": "shard" if world > 1 else "one GPU", "build": w["build"], "search": sp}
+
+
 def run_reference(args, rank, world):
     """The reference has no CPU search; its CPU arm is the CPU restatement of the path (oracle/),
     timed on all host threads on a bounded sample of the same workload."""
@@ -210,12 +267,13 @@ def run_reference(args, rank, world):
         times.append(time.perf_counter() - t0)
     t = statistics.median(times)
     qps = len(sample) / t
+    config = workload_config(args, w, sp, world)
+    config["note"] = ("CPU restatement of the search path (the reference has no CPU search), all copies "
+                      "in this process's memory")
     line = {"impl": "reference", "metric": METRIC, "value": qps, "unit": "queries/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * t,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-            "data": "synthetic",
-            "config": {"workload": args.workload, "search": sp, "build": w["build"], "k": K,
-                       "note": "CPU restatement of the search path (the reference has no CPU search)"},
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16/f32/i8",
+            "data": "synthetic", "config": config,
             "cpu_baseline": {"value": qps, "unit": "queries/s", "cores": cores, "kind": "port",
                              "sample": f"{len(sample)} of {w['nq']} queries per step, same index"},
             "e2e": {"value": qps, "unit": "queries/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
@@ -245,6 +303,85 @@ def emit(line):
         os.write(_STDOUT_FD, data)
 
 
+def timed_resident(idx, nq, sp, steps, warmup, flush, barrier, clocks=None):
+    """`steps` graph replays of the batch already on the GPU, L2 flushed before each; CUDA events on
+    torch's current stream (the library orders its own stream after it and signals back to it).
+    Returns the milliseconds of every step and the wall time of the region."""
+    import torch
+    stream = torch.cuda.current_stream()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    for _ in range(warmup):
+        flush.fill_(1)
+        idx.search_resident(nq, K, stream=stream.cuda_stream, **sp)
+    barrier()
+    if clocks is not None:
+        clocks.begin()
+    wall0 = time.perf_counter()
+    for a, b in ev:
+        flush.fill_(1)  # evict the index from L2 between timed steps
+        a.record(stream)
+        idx.search_resident(nq, K, stream=stream.cuda_stream, **sp)
+        b.record(stream)
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - wall0
+    if clocks is not None:
+        clocks.end()
+    return [a.elapsed_time(b) for a, b in ev], wall
+
+
+def parity_against_checker(idx, arrays_host, meta, queries, ids_run, dist_run, truth, sp, n_sample, parts=1):
+    """The north star's own criteria on a sample of the bench batch: the GPU's answer for the
+    timed path (`ids_run`, `dist_run`: nothing kept for inspection) against the CPU checker started
+    from the GPU's own projected coordinates (the inspected run gives them)."""
+    from oracle import oracle_py
+    sample = queries[:n_sample]
+    idx.set_debug(taps=True)
+    _, ids_tap = idx.search(sample, K, **sp)
+    y = idx.fetch("y", np.uint16, (len(sample), -1))
+    idx.set_debug(taps=False)
+    ox = oracle_py.Index(arrays_host, meta)
+    want_i, want_d, _ = ox.search(sample, K, y_in=y, parts=parts, **sp)
+    got_i, got_d = ids_run[:len(sample)], dist_run[:len(sample)]
+    same = got_i == want_i
+    rel = np.abs(got_d[same] - want_d[same]) / np.maximum(np.abs(want_d[same]), 1e-30)
+    return {"sample_queries": int(len(sample)),
+            "ids_match_frac": float(same.mean()),
+            "ids_match_frac_inspected_run": float((ids_tap == want_i).mean()),
+            "dist_max_rel": float(rel.max()) if rel.size else 0.0,
+            "recall_gpu": recall_of(got_i, truth[:len(sample)]),
+            "recall_oracle": recall_of(want_i, truth[:len(sample)]),
+            "criteria": "ids >= 0.999 of slots, distances within 1e-3 relative, |recall difference| <= 0.002"}
+
+
+def reference_kernels(arrays, meta, idx, queries, ids_run, sp, kernel_ms, steps):
+    """The reference's own search kernels (oracle/_ref/libref_search.so: its search_kernels.cuh
+    compiled unmodified for this GPU) on the same index, batch and parameters, from the GPU's
+    projected coordinates; L2 flushed before each timed stage as for the kernels of this library.
+    Outside the timed region; a report beside the number, like the CPU baseline."""
+    from oracle import oracle_py
+    if oracle_py.ref_search() is None:
+        return {"unavailable": "oracle/_ref/libref_search.so is not built (reference sources not at hand)"}
+    nq = len(queries)
+    idx.set_debug(taps=True)
+    idx.search(queries, K, **sp)
+    y = idx.fetch("y", np.uint16, (nq, -1))
+    qs = idx.fetch("qs", np.float32, (nq, -1))
+    idx.set_debug(taps=False)
+    ref = oracle_py.ref_search_pipeline(arrays, meta, y, qs, queries, K, reps=max(3, min(steps, 10)),
+                                        flush_mb=256, **sp)
+    ours_first = sum(kernel_ms.get(k_, 0.0) for k_ in ("project", "cell_codes", "probe", "round_lists"))
+    ours_waves = kernel_ms.get("round_rows", 0.0) * sp["waves"]
+    ref_first, ref_waves = float(ref["kernel_ms"][0]), float(ref["kernel_ms"][1])
+    return {"first_round_ms": ref_first, "waves_ms": ref_waves,
+            "stages": "cell lookup + gather + rerank-keep | waves x (pick starts + gather + rerank-keep); "
+                      "its projection GEMM (cuBLASLt) is not included",
+            "this_library_first_round_ms": ours_first, "this_library_waves_ms": ours_waves,
+            "this_library_stages": "projection + decode + lookup + first round | waves",
+            "ratio": (ref_first + ref_waves) / max(ours_first + ours_waves, 1e-9),
+            "ids_match_frac": float((ref["best_ids"] == ids_run).mean()),
+            "l2": "256 MB written before each timed stage, median of the repetitions"}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -255,15 +392,15 @@ def main():
     ap.add_argument("--cpu-sample", type=int, default=2000)
     ap.add_argument("--ladder-start", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-ref-kernels", action="store_true")
     ap.add_argument("--copies", type=int, default=0, help="override the copies of the build")
     ap.add_argument("--search", default="", help="JSON search parameters (skips the ladder)")
     ap.add_argument("--queries", type=int, default=0,
                     help="queries per batch instead of the workload's (small profiler captures)")
-    ap.add_argument("--placement", default="replicate", choices=["replicate", "shard", "shard-rows"],
-                    help="with several GPUs: replicate = every GPU answers its own batches (weak "
-                         "scaling, no collective); shard = one batch, copies and the neighbor table "
-                         "split over the GPUs, kept lists exchanged over NCCL (strong scaling); "
-                         "shard-rows = shard with the sketch and the fp16 vectors dealt by rows too")
+    ap.add_argument("--placement", default="shard", choices=["shard", "shard-rows"],
+                    help="with several GPUs: shard = copies and the neighbor table split over the GPUs, "
+                         "kept lists exchanged over NCCL; shard-rows = the sketch and the fp16 vectors "
+                         "dealt by rows too")
     args = ap.parse_args()
     claim_stdout()
     args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
@@ -288,9 +425,9 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     w = WORKLOADS[args.workload]
-    sharded = world > 1 and args.placement != "replicate"  # one batch answered by all GPUs together
+    sharded = world > 1  # one batch answered by all GPUs together
     t0 = time.time()
-    base, queries = make_data(w, 0 if sharded else rank)
+    base, queries = make_data(w, 0)  # every rank draws the same data: one index, one batch
     log(f"[rank {rank}] data {time.time() - t0:.1f}s")
     t0 = time.time()
     arrays, meta = build_index.build_arrays(base, build_index.IndexParams(**w["build"]),
@@ -298,6 +435,7 @@ def main():
                                             verbose=(rank == 0))
     torch.cuda.synchronize()
     log(f"[rank {rank}] index built in {time.time() - t0:.1f}s")
+    whole = octex_b200.attach(arrays, meta, borrow=True)  # the whole index on this GPU
     if sharded:
         from octex_b200 import dist as odist
         rows = args.placement == "shard-rows"
@@ -305,7 +443,7 @@ def main():
                                 shard_vectors=rows, sketch="shard" if rows else "replicate")
         odist.connect(idx)
     else:
-        idx = octex_b200.attach(arrays, meta, borrow=True)
+        idx = whole
     index_bytes = sum(v.numel() * v.element_size() for v in arrays.values())
     nq = len(queries)
     q_dev = torch.as_tensor(queries, device="cuda")
@@ -313,16 +451,14 @@ def main():
 
     # search parameters: the cheapest rung of the ladder that reaches recall@10 >= 0.99
     chosen, rec = None, 0.0
+    ids_run = dist_run = None
     for sp in ([given_search(args)] if args.search else LADDER[args.ladder_start:]):
-        _, ids = idx.search(q_dev, K, **sp)
-        r = recall_of(ids.cpu().numpy(), truth)
+        d_, i_ = idx.search(q_dev, K, **sp)
+        r = recall_of(i_.cpu().numpy(), truth)
         log(f"[rank {rank}] {sp} recall@10 {r:.4f}")
-        if world > 1:  # every rank has its own queries: all take the rung the worst of them needs
-            t = torch.tensor([r], device="cuda", dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MIN)
-            r = float(t[0])
         if r > rec:
             chosen, rec = sp, r
+            ids_run, dist_run = i_.cpu().numpy(), d_.cpu().numpy()
         if r >= 0.99:
             break
     sp = chosen
@@ -330,11 +466,11 @@ def main():
     # per-query counters of what the kernels read, for the algorithmic bytes
     idx.set_debug(stats=True)
     idx.search(q_dev, K, **sp)
-    stats = idx.fetch("stats", np.int64, (nq, 8))
+    stats = idx.fetch("stats", np.int64, (-1, 8))
     idx.set_debug(stats=False)
-    alg = algorithmic_bytes(stats, sp, meta, K)
+    local_meta = dict(meta, copies=meta["copies"] // world if sharded else meta["copies"])
+    alg = algorithmic_bytes(stats, sp, local_meta, K)
 
-    stream = torch.cuda.current_stream()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")  # > L2 (126 MB)
 
     def barrier():
@@ -344,24 +480,9 @@ def main():
 
     # ---- value: queries resident on the GPU, one graph replay per step ----
     idx.search(q_dev, K, **sp)  # leaves the batch on the GPU
-    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
-          for _ in range(args.steps)]
-    with ClockSampler(local) as clocks:
-        for _ in range(args.warmup):
-            flush.fill_(1)
-            idx.search_resident(nq, K, stream=stream.cuda_stream, **sp)
-        barrier()
-        clocks.begin()
-        wall0 = time.perf_counter()
-        for a, b in ev:
-            flush.fill_(1)  # evict the index from L2 between timed steps
-            a.record(stream)
-            idx.search_resident(nq, K, stream=stream.cuda_stream, **sp)
-            b.record(stream)
-        torch.cuda.synchronize()
-        wall = time.perf_counter() - wall0
-        clocks.end()
-    step_ms = [a.elapsed_time(b) for a, b in ev]
+    uuid = str(getattr(torch.cuda.get_device_properties(local), "uuid", "") or "")
+    with ClockSampler(local, uuid) as clocks:
+        step_ms, wall = timed_resident(idx, nq, sp, args.steps, args.warmup, flush, barrier, clocks)
     total_ms = sum(step_ms)
     barrier()
 
@@ -390,6 +511,39 @@ def main():
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - e0
     rec_e2e = recall_of(on, truth)
+    e2e_same = bool(np.array_equal(on, ids_run))
+
+    # ---- several GPUs: what the sharded answer is worth, and the replica figure beside it ----
+    multi = {}
+    if sharded:
+        # (a) the same batch answered by this GPU alone from the whole index
+        _, i_one = whole.search(q_dev, K, **sp)
+        i_one = i_one.cpu().numpy()
+        multi["ids_match_one_gpu"] = float((i_one == ids_run).mean())
+        multi["recall_one_gpu"] = recall_of(i_one, truth)
+        # (b) N independent replicas, every GPU its own batches, no collective (secondary figure)
+        whole.search(q_dev, K, **sp)
+        rep_ms, _ = timed_resident(whole, nq, sp, args.steps, args.warmup, flush, barrier)
+        t = torch.tensor([sum(rep_ms)], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        multi["replicas_qps"] = world * nq * args.steps / (float(t[0]) * 1e-3)
+        multi["replicas_note"] = ("every GPU holds the whole index and answers its own batches: weak "
+                                  "scaling, no data-path collective; not the headline value")
+        # (c) the sharded search against the CPU checker in its sharded mode (first round per part,
+        # merge of the parts' kept lists), bit for bit: the dimension-ordered projection gives
+        # coordinates the checker reproduces itself
+        ns = min(500, nq)
+        idx.set_projection(ordered=True)
+        d_s, i_s = idx.search(queries[:ns], K, **sp)
+        idx.set_projection(ordered=False)
+        if rank == 0:
+            from oracle import oracle_py
+            host = {k_: v.cpu().numpy() for k_, v in arrays.items()}
+            want_i, want_d, _ = oracle_py.Index(host, meta).search(queries[:ns], K, parts=world, **sp)
+            multi["ids_match_checker_parts"] = float((want_i == i_s).mean())
+            multi["dist_equal_checker_parts"] = bool(np.array_equal(want_d.view(np.uint32), d_s.view(np.uint32)))
+            multi["checker_sample_queries"] = ns
+            del host
 
     if world > 1:
         t = torch.tensor([total_ms, e2e_s * 1e3], device="cuda", dtype=torch.float64)
@@ -398,16 +552,23 @@ def main():
         r = torch.tensor([rec, rec_e2e], device="cuda", dtype=torch.float64)
         dist.all_reduce(r, op=dist.ReduceOp.MIN)
         rec, rec_e2e = float(r[0]), float(r[1])
+        # per-kernel milliseconds of every rank (the slowest rank sets the pace of a stage)
+        names = sorted(kernel_ms)
+        km = torch.tensor([kernel_ms[n_] for n_ in names], device="cuda", dtype=torch.float64)
+        dist.all_reduce(km, op=dist.ReduceOp.MAX)
+        kernel_ms_max = {n_: float(v) for n_, v in zip(names, km)}
     else:
         e2e_ms = e2e_s * 1e3
+        kernel_ms_max = kernel_ms
     if rank != 0:
+        if sharded:
+            idx.close()
         if world > 1:
             dist.destroy_process_group()
         return
 
-    batches = 1 if sharded else world  # batches answered per step over all GPUs
-    qps = batches * nq * args.steps / (total_ms * 1e-3)
-    e2e_qps = batches * nq * args.steps / (e2e_ms * 1e-3)
+    qps = nq * args.steps / (total_ms * 1e-3)
+    e2e_qps = nq * args.steps / (e2e_ms * 1e-3)
     peaks = {}
     try:
         peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
@@ -429,21 +590,27 @@ def main():
                 "kernel_ms": kernel_ms,
                 "kernels": {k_: {"GB/s": alg[k_] / (kernel_ms[k_] * 1e-3) / 1e9,
                                  "frac": alg[k_] / (kernel_ms[k_] * 1e-3) / 1e9 / peak} for k_ in timed}}
-    line = {
-        "metric": METRIC, "value": qps, "unit": "queries/s", "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
-        "scaling": "strong" if sharded else "weak", "vs_baseline": None, "dtype": "f16/f32/i8",
-        "data": "synthetic",
-        "config": {"workload": args.workload, "n": w["n"], "dim": w["dim"], "queries_per_step": nq,
-                   "k": K, "placement": args.placement if world > 1 else "one GPU", "build": w["build"], "search": sp,
-                   "recall_at_10": rec, "recall_at_10_e2e": rec_e2e,
+    if sharded:
+        roofline["kernel_ms_slowest_rank"] = kernel_ms_max
+        roofline["note"] = ("round_rows here = exchange of the kept lists (NCCL send / receive) + merge + "
+                            "the wave of this GPU's slice; best_k includes the gathering of the results")
+    config = workload_config(args, w, sp, world)
+    config.update({"recall_at_10": rec, "recall_at_10_e2e": rec_e2e, "e2e_ids_equal_resident": e2e_same,
                    "index_bytes": index_bytes, "l2": "flushed between timed steps (256 MB fill)",
+                   "memory_report": idx.memory_report(),
                    "mean_per_query": {"levels_tried": float(stats[:, 0].mean()),
                                       "list_entries": float(stats[:, 2].mean()),
                                       "distinct_first_round": float(stats[:, 3].mean()),
                                       "table_rows": float(stats[:, 4].mean()),
                                       "distinct_waves": float(stats[:, 5].mean()),
-                                      "rows_reranked": float(stats[:, 6].mean())}},
+                                      "rows_reranked": float(stats[:, 6].mean())}})
+    if sharded and args.placement != "shard":
+        config["placement"] = args.placement
+    line = {
+        "metric": METRIC, "value": qps, "unit": "queries/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f16/f32/i8",
+        "data": "synthetic", "config": config,
         "clocks": clocks.summary(),
         "e2e": {"value": e2e_qps, "unit": "queries/s",
                 "h2d_bytes_per_step": int(queries.nbytes),
@@ -452,20 +619,35 @@ def main():
         "wall_s_timed_region": wall,
         "roofline": roofline,
     }
-    if not args.no_cpu_baseline and world == 1:  # the CPU leg is timed once, beside the one-GPU run
-        try:
-            line["cpu_baseline"] = cpu_baseline(arrays, meta, queries, sp, args)
-        except Exception as e:  # the baseline is a report, never a reason to lose the GPU numbers
-            line["cpu_baseline"] = {"value": None, "error": str(e)}
+    if multi:
+        line["multi_gpu"] = multi
+    if world == 1:  # the comparison legs run once, beside the one-GPU number
+        host = None
+        if not args.no_cpu_baseline:
+            try:
+                host = {k_: v.cpu().numpy() for k_, v in arrays.items()}
+                line["cpu_baseline"] = cpu_baseline(host, meta, queries, sp, args)
+                line["parity"] = parity_against_checker(idx, host, meta, queries, ids_run, dist_run, truth,
+                                                        sp, args.cpu_sample)
+            except Exception as e:  # a report, never a reason to lose the GPU numbers
+                line.setdefault("cpu_baseline", {"value": None, "error": str(e)})
+                line.setdefault("parity", {"error": str(e)})
+        if not args.no_ref_kernels:
+            try:
+                line["ref_kernels"] = reference_kernels(arrays, meta, idx, queries, ids_run, sp,
+                                                        kernel_ms, args.steps)
+            except Exception as e:
+                line["ref_kernels"] = {"error": str(e)}
     emit(line)
+    if sharded:
+        idx.close()
     if world > 1:
         dist.destroy_process_group()
 
 
-def cpu_baseline(arrays, meta, queries, sp, args):
+def cpu_baseline(host, meta, queries, sp, args):
     """The CPU restatement of the path timed on this box's host cores on a bounded sample."""
     from oracle import oracle_py
-    host = {k_: v.cpu().numpy() for k_, v in arrays.items()}
     ox = oracle_py.Index(host, meta)
     sample = queries[:args.cpu_sample]
     ox.search(sample[:64], K, **sp)

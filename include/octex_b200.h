@@ -199,6 +199,12 @@ OCTEX_B200_EXPORT cuvsError_t octexB200LoadRank(cuvsResources_t res, const char*
  * the kernels then read with plain loads. A search before this call fails and says so. */
 OCTEX_B200_EXPORT cuvsError_t octexB200CommUniqueId(void* id128);
 OCTEX_B200_EXPORT cuvsError_t octexB200CommInit(cuvsOctexIndex_t index, const void* id128);
+/* The way out of octexB200CommInit, a COLLECTIVE like it: every process of the index calls it
+ * before it destroys its handle. Each process drops its plans, waits for its stream, unmaps the
+ * row ranges of the other processes, and returns only after all processes have unmapped (so none
+ * frees memory that another still has mapped); the communicator is destroyed. (The reference needs
+ * no such call: its one process owns every GPU's memory, cpp/src/neighbors/octex/load.cu:187-202.) */
+OCTEX_B200_EXPORT cuvsError_t octexB200CommDisconnect(cuvsOctexIndex_t index);
 
 /* The arrays of an index directory handed over in memory (host or device pointers), with the
  * dtypes and shapes of docs/design.md:27-48. */
@@ -248,6 +254,19 @@ OCTEX_B200_EXPORT cuvsError_t octexB200ProfileBatch(cuvsResources_t res,
                                                     int64_t k, float* ms, int32_t capacity,
                                                     int32_t* count);
 
+/* Waits for the index's stream and reports, once, whether a kernel of the searches queued so far
+ * gave up (the bounded waits of the tensor-core projection): CUVS_ERROR with a message, else
+ * CUVS_SUCCESS. A search with host outputs checks by itself; after a search with device outputs
+ * (cuvsOctexSearch on device tensors: results are only ordered on the stream of `res`,
+ * c/include/cuvs/neighbors/octex.h:283-289 of the reference) this is the call that tells. */
+OCTEX_B200_EXPORT cuvsError_t octexB200CheckLast(cuvsOctexIndex_t index);
+
+/* detail::memory_report (cpp/src/neighbors/octex/search.cu:999-1016): device memory of this
+ * process's GPU by index part. bytes[7] = device ordinal, copies (lists, cell tables, base), sketch,
+ * table, vectors, other (projections, sketch basis, pointer tables), batch buffers of the cached
+ * search configuration. Arrays kept in host memory count 0. */
+OCTEX_B200_EXPORT cuvsError_t octexB200MemoryReport(cuvsOctexIndex_t index, int64_t* bytes);
+
 /* Observation (detail::timed_batch / memory_report, search.cu:965-1016, are the reference's
  * counterparts): stats = per-query counters of what the kernels read, taps = keep the intermediate
  * arrays of the last batch. Either one changes the plan; both are off by default. */
@@ -280,7 +299,15 @@ OCTEX_B200_EXPORT cuvsError_t octexB200CellCodes(const float* y, int64_t n, int3
  * queries [n_queries, dim] float32 and codes [n_queries, copies, levels] int64 are DEVICE memory on
  * the GPU of the index, which must be the current device; the work is queued on `stream` (a
  * cudaStream_t, NULL for the default stream) and codes[q][c][j] is the code of query q's cell in
- * copy c at spacing j, every level computed (the array octexB200Fetch calls "codes").
+ * copy c at spacing j, every level computed. The coordinates behind these codes come from the
+ * projection that sums in dimension order (octexB200SetProjection(index, 1)); they are the array
+ * octexB200Fetch calls "codes" bit for bit when the search uses that projection too, which it does
+ * after octexB200SetProjection(index, 1) and for every index whose copies do not have 4 blocks.
+ * The default search of a 4-block index projects on the tensor cores, whose fp32 sums run in another
+ * order: about 1 % of its fp16 coordinates land on the neighbouring fp16 value, so a small share of
+ * its codes (a few per cent at the finest spacing) name a neighbouring cell. An index whose copies
+ * are dealt over several processes (shard placement, world > 1) is refused: the call answers for
+ * all copies of an index or not at all.
  *
  * The intermediates (centred fp16 queries, sketch-space queries, fp16 projected coordinates) live
  * in one fixed 32 MiB array inside the library, which every GPU that loads the library holds until
@@ -288,9 +315,10 @@ OCTEX_B200_EXPORT cuvsError_t octexB200CellCodes(const float* y, int64_t n, int3
  * bytes (dim64 = dim rounded up to 64) exceed 32 MiB is refused with CUVS_ERROR and a message that
  * names the largest batch that fits. All calls on a GPU share that array: it holds whatever the
  * last call left (each call overwrites every byte it later reads, nothing needs clearing), and two
- * calls that overlap on the GPU (different streams, no ordering between them) race on it. The
- * first call on each GPU looks up the array's device address; make that first call outside of any
- * stream capture. */
+ * calls that overlap on the GPU (different streams, no ordering between them) race on it. Every
+ * call asks the runtime for the array's address on the current device (so the call stays valid
+ * after a cudaDeviceReset); the first time that happens on a GPU the library's device code is
+ * loaded there, so make the first call on each GPU outside of any stream capture. */
 OCTEX_B200_EXPORT cuvsError_t octexB200QueryCodesStatic(cuvsOctexIndex_t index,
                                                         const float* queries, int64_t n_queries,
                                                         int64_t* codes, void* stream);

@@ -90,7 +90,8 @@ SYMBOLS = (
     "cuvsOctexSearch", "octexB200Search", "octexB200LoadRank", "octexB200Attach",
     "octexB200SearchResident", "octexB200ProfileBatch", "octexB200SetDebug", "octexB200Fetch",
     "octexB200CellCodes", "octexB200QueryCodesStatic", "octexB200SetProjection",
-    "octexB200CommUniqueId", "octexB200CommInit",
+    "octexB200CommUniqueId", "octexB200CommInit", "octexB200CommDisconnect", "octexB200CheckLast",
+    "octexB200MemoryReport",
 )
 
 

@@ -10,7 +10,9 @@
 #include <octex_b200.hpp>
 
 #include <cstring>
+#include <memory>
 #include <string>
+#include <vector>
 
 namespace {
 
@@ -84,6 +86,19 @@ auto as_index(cuvsOctexIndex const& index) -> octex_b200::index*
 {
   OCTEX_EXPECTS(index.addr != 0, "octex: the index is empty (load it first)");
   return reinterpret_cast<octex_b200::index*>(index.addr);
+}
+
+/// Report (once) a kernel of the last batches that gave up; the stream of the index is idle.
+void check_last(octex_b200::detail::index_impl& ix)
+{
+  std::vector<std::shared_ptr<octex_b200::detail::plan>> plans;
+  {
+    std::lock_guard<std::mutex> lock(ix.mu);
+    for (auto const& kv : ix.plans)
+      plans.push_back(kv.second);
+  }
+  for (auto const& pl : plans)
+    octex_b200::detail::check_tc(*pl);
 }
 
 template <typename T>
@@ -402,6 +417,37 @@ cuvsError_t octexB200SearchResident(cuvsResources_t res, cuvsOctexSearchParams_t
     octex_b200::detail::search_impl(as_res(res), p, ix, nullptr, n_queries, ix.dim(), nullptr,
                                     nullptr, k, false, true);
     OCTEX_CUDA_TRY(cudaStreamSynchronize(ix.impl().part.stream));
+    check_last(ix.impl());
+  });
+}
+
+cuvsError_t octexB200CheckLast(cuvsOctexIndex_t index)
+{
+  return translate([=] {
+    auto& ix = as_index(*index)->impl();
+    OCTEX_CUDA_TRY(cudaStreamSynchronize(ix.part.stream));
+    check_last(ix);
+  });
+}
+
+cuvsError_t octexB200MemoryReport(cuvsOctexIndex_t index, int64_t* bytes)
+{
+  return translate([=] {
+    OCTEX_EXPECTS(bytes != nullptr, "octex: a NULL report");
+    auto& ix = as_index(*index)->impl();
+    auto const& p = ix.part;
+    auto dev = [](octex_b200::dbuf const& b) { return b.host ? int64_t{0} : static_cast<int64_t>(b.size); };
+    bytes[0] = p.device;
+    bytes[1] = dev(p.lists) + dev(p.base) + dev(p.cell_table) + dev(p.cell_off) + dev(p.cell_mask) + dev(p.level_on);
+    bytes[2] = dev(p.sketch);
+    bytes[3] = dev(p.table);
+    bytes[4] = dev(p.vectors);
+    bytes[5] = dev(p.ut) + dev(p.shift) + dev(p.inv_f) + dev(p.mean) + dev(p.basis) + dev(p.scale) +
+               dev(p.table_rows.ptrs) + dev(p.sketch_rows.ptrs) + dev(p.vector_rows.ptrs);
+    bytes[6] = 0;
+    std::lock_guard<std::mutex> lock(ix.mu);
+    for (auto const& kv : ix.plans)
+      bytes[6] += kv.second->buffer_bytes;
   });
 }
 
@@ -453,6 +499,14 @@ cuvsError_t octexB200CommInit(cuvsOctexIndex_t index, const void* id128)
                                                                    ix.part.device);
     }
     octex_b200::detail::connect_rows(ix);  // arrays dealt by rows: map the other processes' ranges
+  });
+}
+
+cuvsError_t octexB200CommDisconnect(cuvsOctexIndex_t index)
+{
+  return translate([=] {
+    auto& ix = as_index(*index)->impl();
+    octex_b200::detail::disconnect_rows(ix);
   });
 }
 

@@ -76,8 +76,8 @@ struct device_part {
     int cur = 0;
     cudaGetDevice(&cur);
     cudaSetDevice(device);
-    // nothing of this process reads the other processes' memory any more (a search returns after
-    // every process has sent its results, so none of them is still reading this one's either)
+    // mappings still open here were not released by disconnect_rows (the collective way out):
+    // closing them is all a single process can do
     for (dealt_rows* d : {&table_rows, &sketch_rows, &vector_rows})
       for (void* p : d->opened)
         cudaIpcCloseMemHandle(p);
@@ -113,5 +113,10 @@ void place(index_impl& ix, source_arrays const& src);
 /// After the communicator exists: exchange the addresses of the row ranges dealt over the
 /// processes (a collective: every process calls it).
 void connect_rows(index_impl& ix);
+/// The way back, also a collective: every process drops its plans, waits for its own stream,
+/// unmaps the other processes' ranges, and only after all of them have done so (a barrier on the
+/// communicator) does any of them go on to free the range it exported; the communicator goes last.
+/// Without it a process that closes early would free memory another still has mapped.
+void disconnect_rows(index_impl& ix);
 
 }  // namespace octex_b200::detail

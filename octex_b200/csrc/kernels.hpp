@@ -30,6 +30,9 @@ __host__ __device__ inline int hash_slots_of(int total, int cap, int twelfths)
 /// Rows [from, m) of q become copies of row 0 (padding of a partial batch).
 void pad_rows(float* q, int from, int m, int D, cudaStream_t s);
 
+/// Largest dimension center_sketch takes: its block keeps 16 centred rows in shared memory.
+constexpr int kMaxDim = (227 << 10) / (16 * 4);
+
 /// qh [m, ldq] = half(q - mean) zero-padded to ldq columns; qs [m, S] = (q - mean) @ basis in fp32
 /// (one fused multiply-add per dimension, in dimension order).
 void center_sketch(const float* q, const float* mean, const float* basis, int m, int D, int S,

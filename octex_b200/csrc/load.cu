@@ -113,6 +113,8 @@ void place(index_impl& ix, source_arrays const& src)
   const int64_t D = ix.dim, N = ix.n, S = ix.sketch_width;
   const int64_t T1 = (int64_t{1} << ix.log_buckets) + 1;
   OCTEX_EXPECTS(ix.dim % 2 == 0, "octex: the dimension must be even");
+  OCTEX_EXPECTS(ix.dim <= kernels::kMaxDim,
+                "octex: dimensions above " + std::to_string(kernels::kMaxDim) + " are not supported");
   OCTEX_EXPECTS(ix.sketch_width % 16 == 0 && ix.sketch_width <= 512 && ix.sketch_width > 0,
                 "octex: sketch width: a multiple of 16, <= 512");
   OCTEX_EXPECTS((ix.blocks >= 1 && ix.blocks <= 6) || ix.blocks == 8,
@@ -382,6 +384,29 @@ void connect_rows(index_impl& ix)
   ix.plans.clear();  // plans made before the connection do not know the tables
 }
 
+void disconnect_rows(index_impl& ix)
+{
+  auto& p = ix.part;
+  if (ix.world <= 1 || ix.comm == nullptr) return;
+  OCTEX_CUDA_TRY(cudaSetDevice(p.device));
+  {
+    std::lock_guard<std::mutex> lock(ix.mu);
+    ix.plans.clear();  // their graphs hold the exchanges and the addresses of the mapped ranges
+  }
+  OCTEX_CUDA_TRY(cudaStreamSynchronize(p.stream));
+  for (dealt_rows* d : {&p.table_rows, &p.sketch_rows, &p.vector_rows}) {
+    for (void* q : d->opened)
+      OCTEX_CUDA_TRY(cudaIpcCloseMemHandle(q));
+    d->opened.clear();
+    d->ptrs = dbuf();
+  }
+  // nobody frees an exported range before everybody has unmapped it
+  dbuf one(p.device, 1), all(p.device, static_cast<size_t>(ix.world));
+  ix.comm->all_gather(one.ptr, all.ptr, 1, p.stream);
+  OCTEX_CUDA_TRY(cudaStreamSynchronize(p.stream));
+  ix.comm.reset();
+}
+
 }  // namespace detail
 
 index::index(std::shared_ptr<detail::index_impl> impl) : impl_(std::move(impl)) {}
@@ -397,13 +422,25 @@ auto index::impl() const noexcept -> detail::index_impl& { return *impl_; }
 
 namespace {
 
-void choose_device(detail::index_impl& ix, load_params const& params)
+void choose_device(detail::index_impl& ix, load_params const& params, bool from_directory)
 {
   OCTEX_EXPECTS(params.mode == placement::replicate || params.mode == placement::shard,
                 "octex: placement must be replicate or shard");
   int cur = 0;
   OCTEX_CUDA_TRY(cudaGetDevice(&cur));
   if (params.devices.empty()) {
+    // The reference places an index on every visible GPU when none is named
+    // (cpp/src/neighbors/octex/load.cu:241-251). This library drives one GPU per process, so a
+    // caller of the reference's load on a machine with several GPUs must say which one it means
+    // rather than silently get one of them; a process that states its rank among several
+    // (load_params::world > 1) has said so.
+    int visible = 1;
+    OCTEX_CUDA_TRY(cudaGetDeviceCount(&visible));
+    OCTEX_EXPECTS(!from_directory || visible <= 1 || params.world > 1,
+                  "octex: " + std::to_string(visible) +
+                    " GPUs are visible and load_params::devices names none: this library drives one "
+                    "GPU per process; name the device (devices = {d}), or start one process per GPU "
+                    "and give each its rank and world");
     ix.devices = {cur};
   } else {
     OCTEX_EXPECTS(params.devices.size() == 1,
@@ -446,7 +483,7 @@ auto load(resources const& res, std::string const& path, load_params const& para
     }
     return path + "/" + name + ".npy";
   };
-  choose_device(ix, params);
+  choose_device(ix, params, true);
 
   npy_file lists(file("lists")), keys(file("keys")), offsets(file("offsets")), base(file("base"));
   npy_file proj(file("proj")), shift(file("shift")), mean(file("mean"));
@@ -524,7 +561,7 @@ auto attach(resources const& res, index_arrays const& arrays, load_params const&
                   arrays.offsets && arrays.base && arrays.basis && arrays.scale && arrays.sketch &&
                   arrays.vectors,
                 "octex: an index array is missing");
-  choose_device(ix, params);
+  choose_device(ix, params, false);
   detail::source_arrays src;
   src.a          = arrays;
   src.all_copies = arrays.copies;

@@ -359,11 +359,10 @@ void center_sketch(const float* q, const float* mean, const float* basis, int m,
 {
   if (m <= 0) return;
   const size_t smem = sizeof(float) * kCenterRows * D;
-  static size_t allowed = 48 << 10;
-  if (smem > allowed) {
+  // the opt-in belongs to the current device's context: asked for at every launch that needs it
+  // (a host-side call, no stream work), so a process that places indexes on several GPUs is covered
+  if (smem > (48 << 10))
     cudaFuncSetAttribute(center_sketch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    allowed = smem;
-  }
   center_sketch_kernel<<<(m + kCenterRows - 1) / kCenterRows, 128, smem, s>>>(q, mean, basis, m, D, S, qh,
                                                                              ldq, qs);
 }

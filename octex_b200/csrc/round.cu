@@ -1178,12 +1178,9 @@ void merge_kept(const long long* src_i, const float* src_d, int nsrc, int64_t sr
                 int P, int m, long long* si, float* sd, cudaStream_t s)
 {
   if (m <= 0) return;
-  static bool allowed = false;
-  const size_t smem   = sizeof(int) * (2 * static_cast<size_t>(P) + 16);
-  if (!allowed) {
+  const size_t smem = sizeof(int) * (2 * static_cast<size_t>(P) + 16);
+  if (smem > (48 << 10))  // per device and context, so asked for whenever it is needed
     cudaFuncSetAttribute(merge_kept_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 4096 + 64);
-    allowed = true;
-  }
   merge_kept_kernel<<<m, kRoundThreads, smem, s>>>(src_i, src_d, nsrc, src_stride, KO, P, si, sd);
 }
 

@@ -105,16 +105,21 @@ plan::~plan()
   cudaSetDevice(device);
   if (graph != nullptr) cudaGraphExecDestroy(graph);
   if (done_ev != nullptr) cudaEventDestroy(done_ev);
+  if (start_ev != nullptr) cudaEventDestroy(start_ev);
   if (tc_error_host != nullptr) cudaFreeHost(tc_error_host);
   cudaSetDevice(cur);
 }
 
-/// A wait inside the tensor-core projection gave up (it never does unless the GPU misbehaves).
+/// A wait inside the tensor-core projection gave up (it never does unless the GPU misbehaves):
+/// report it once and clear the word, so that one event does not poison the calls after it. Call
+/// it when the stream of the plan is idle.
 void check_tc(plan const& pl)
 {
-  OCTEX_EXPECTS(pl.tc_error_host == nullptr || *pl.tc_error_host == 0,
-                "octex: the projection kernel gave up waiting for its operands (code " +
-                  std::to_string(pl.tc_error_host ? *pl.tc_error_host : 0) + ")");
+  if (pl.tc_error_host == nullptr || *pl.tc_error_host == 0) return;
+  const int code    = *pl.tc_error_host;
+  *pl.tc_error_host = 0;
+  throw error("octex: the projection kernel gave up waiting for its operands (code " +
+              std::to_string(code) + "); the results of that batch are not valid");
 }
 
 /// Launch every kernel of a batch on s (captured into the graph, or run directly).
@@ -514,10 +519,20 @@ void search_impl(resources const& res,
   const int D    = static_cast<int>(ix.dim);
   auto& p        = ix.part;
   cudaStream_t s = p.stream;
+  // a search with device outputs returns before its kernels ran; had one of them given up, the
+  // word is still set and this is the first host code to see it
+  check_tc(*pl);
 
   // the work of this call starts after what the caller queued on its stream (search.cu:841-848)
-  cudaEvent_t start = nullptr;
-  OCTEX_CUDA_TRY(cudaEventCreateWithFlags(&start, cudaEventDisableTiming));
+  // an event of the plan (one search at a time uses it: pl->mu), on the device of the caller's
+  // stream, which is the current one
+  if (pl->start_ev == nullptr || pl->start_dev != cur) {
+    if (pl->start_ev != nullptr) cudaEventDestroy(pl->start_ev);
+    pl->start_ev = nullptr;
+    OCTEX_CUDA_TRY(cudaEventCreateWithFlags(&pl->start_ev, cudaEventDisableTiming));
+    pl->start_dev = cur;
+  }
+  cudaEvent_t start = pl->start_ev;
   OCTEX_CUDA_TRY(cudaEventRecord(start, caller));
   OCTEX_CUDA_TRY(cudaSetDevice(p.device));
   OCTEX_CUDA_TRY(cudaStreamWaitEvent(s, start, 0));
@@ -565,7 +580,6 @@ void search_impl(resources const& res,
   OCTEX_CUDA_TRY(cudaSetDevice(cur));
   OCTEX_CUDA_TRY(cudaStreamWaitEvent(caller, pl->done_ev, 0));
   if (host_out) OCTEX_CUDA_TRY(cudaStreamSynchronize(caller));
-  OCTEX_CUDA_TRY(cudaEventDestroy(start));
   if (host_out) check_tc(*pl);
 }
 

@@ -40,6 +40,8 @@ struct plan {
   size_t smem_max       = 0;
   cudaGraphExec_t graph = nullptr;
   cudaEvent_t done_ev   = nullptr;
+  cudaEvent_t start_ev  = nullptr;  // recorded on the caller's stream at the start of a search
+  int start_dev         = -1;       // device it was created on
   int64_t buffer_bytes  = 0;
   std::mutex mu;  // one search at a time per plan
   ~plan();
@@ -64,6 +66,10 @@ void search_impl(resources const& res,
 /// best k (the per-kernel counterpart of detail::timed_batch, search.cu:965-981 of the reference).
 auto profile_batch(resources const& res, search_params const& sp, index const& idx, int64_t nq,
                    int64_t k) -> std::vector<float>;
+
+/// Throws when a kernel of an earlier batch of this plan reported that it gave up (and clears the
+/// report).
+void check_tc(plan const& pl);
 
 auto get_plan(index_impl& ix, search_params const& sp, int m, int k) -> std::shared_ptr<plan>;
 

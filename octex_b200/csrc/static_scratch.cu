@@ -18,7 +18,6 @@
 #include <octex_b200.h>
 
 #include <algorithm>
-#include <mutex>
 #include <string>
 
 namespace {
@@ -29,32 +28,24 @@ namespace {
 constexpr size_t kScratchBytes = size_t{32} << 20;
 
 /// The intermediates of octexB200QueryCodesStatic. In host code this name is only a handle for
-/// cudaGetSymbolAddress; the address kernels can use is looked up per device in scratch_of().
+/// cudaGetSymbolAddress; the address kernels can use is looked up in scratch_of_current_device().
 static __device__ __align__(256) unsigned char g_static_scratch[kScratchBytes];
 
-constexpr int kMaxDevices = 64;
-std::mutex g_setup_mutex;
-void* g_scratch_of_device[kMaxDevices] = {};
-
-/// Device address of the static array on the current device `dev`; looked up on the first call
-/// on that device (the lookup loads the module on the device, which is why the first call should
-/// happen outside of any stream capture) and remembered.
-auto scratch_of(int dev) -> unsigned char*
+/// Device address of the static array on the current device. Asked for at every call: the
+/// address belongs to the current device's context (it changes after a cudaDeviceReset), the lookup
+/// is cheap once the module is loaded, and the first lookup on a device loads the module there,
+/// which is why the first call on a device should happen outside of any stream capture.
+auto scratch_of_current_device() -> unsigned char*
 {
-  OCTEX_EXPECTS(dev >= 0 && dev < kMaxDevices, "octex: device ordinal out of range");
-  std::lock_guard<std::mutex> lock(g_setup_mutex);
-  if (g_scratch_of_device[dev] == nullptr) {
-    void* p       = nullptr;
-    cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
-    if (e != cudaSuccess) {
-      cudaGetLastError();
-      throw octex_b200::error(std::string("octex: cudaGetSymbolAddress of the static scratch: ") +
-                              cudaGetErrorString(e));
-    }
-    OCTEX_EXPECTS(p != nullptr, "octex: the static scratch has no device address");
-    g_scratch_of_device[dev] = p;
+  void* p       = nullptr;
+  cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    throw octex_b200::error(std::string("octex: cudaGetSymbolAddress of the static scratch: ") +
+                            cudaGetErrorString(e));
   }
-  return static_cast<unsigned char*>(g_scratch_of_device[dev]);
+  OCTEX_EXPECTS(p != nullptr, "octex: the static scratch has no device address");
+  return static_cast<unsigned char*>(p);
 }
 
 auto align_up(size_t v, size_t a) -> size_t { return (v + a - 1) / a * a; }
@@ -78,6 +69,10 @@ extern "C" cuvsError_t octexB200QueryCodesStatic(cuvsOctexIndex_t index, const f
     int dev = -1;
     OCTEX_CUDA_TRY(cudaGetDevice(&dev));
     OCTEX_EXPECTS(dev == p.device, "octex: the current device is not the device of the index");
+    OCTEX_EXPECTS(p.copies == ix.copies,
+                  "octex: this process holds " + std::to_string(p.copies) + " of the index's " +
+                    std::to_string(ix.copies) + " copies (shard placement over several processes); "
+                    "the static-scratch call answers for whole indexes only");
     const int D = static_cast<int>(ix.dim), sw = ix.sketch_width;
     const int L = static_cast<int>(ix.spacings.size());
     const int N = 8 * ix.blocks * p.copies;
@@ -97,7 +92,7 @@ extern "C" cuvsError_t octexB200QueryCodesStatic(cuvsOctexIndex_t index, const f
                               " queries per call for this index)");
     }
     OCTEX_EXPECTS(n_queries <= 0x7fffffff / std::max(N, 1), "octex: too many queries for one call");
-    unsigned char* base = scratch_of(dev);
+    unsigned char* base = scratch_of_current_device();
     auto* qh            = reinterpret_cast<__half*>(base + qh_off);
     auto* qs            = reinterpret_cast<float*>(base + qs_off);
     auto* Y             = reinterpret_cast<__half*>(base + y_off);

@@ -45,4 +45,5 @@ def connect(index, group=None):
                                group=group)
     raw = (C.c_ubyte * 128).from_buffer_copy(ident[0])
     _lib.check(_lib.lib().octexB200CommInit(index._h, raw))
+    index._connected = True  # Index.close() is a collective from here on
     return index

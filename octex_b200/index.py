@@ -154,6 +154,8 @@ class Index:
         self._h = handle
         self._path = None if path is None else os.fspath(path)
         self._keep = keep  # arrays borrowed by the library live as long as the index
+        self._connected = False  # set by octex_b200.dist.connect
+        self._res = {}  # cuvsResources per caller stream, made once
 
     def _get(self, fn, ctype):
         v = ctype(0)
@@ -202,9 +204,33 @@ class Index:
                 f"devices={self.devices})")
 
     def close(self):
+        """Release the index.  For an index connected to other processes
+        (``octex_b200.dist.connect``) this is a collective: every process calls it, and each
+        returns only after all have unmapped the others' row ranges."""
         if self._h is not None:
+            if self._connected:
+                self._connected = False
+                _lib.check(_lib.lib().octexB200CommDisconnect(self._h))
             _lib.lib().cuvsOctexIndexDestroy(self._h)
             self._h = None
+
+    def _resources(self, stream):
+        res = self._res.get(stream)
+        if res is None:
+            if len(self._res) > 16:
+                self._res.clear()
+            res = self._res[stream] = _Resources(stream)
+        return res
+
+    def memory_report(self):
+        """Device memory of this process's GPU by index part, in bytes (``detail::memory_report``,
+        cpp/src/neighbors/octex/search.cu:999-1016 of the reference): ``device``, ``copies``,
+        ``sketch``, ``table``, ``vectors``, ``other``, and ``buffers`` of the cached search
+        configuration.  Arrays kept in host memory count 0."""
+        out = (C.c_int64 * 7)()
+        _lib.check(_lib.lib().octexB200MemoryReport(self._h, out))
+        names = ("device", "copies", "sketch", "table", "vectors", "other", "buffers")
+        return dict(zip(names, (int(v) for v in out)))
 
     def save(self, path):
         """Copy the index directory to ``path`` (a new or empty directory); ``load(path)`` restores
@@ -220,6 +246,7 @@ class Index:
 
     def __del__(self):
         try:
+            self._connected = False  # no collective from a finaliser: the others may be gone
             self.close()
         except Exception:
             pass
@@ -287,12 +314,13 @@ class Index:
         for given in (neighbors, distances):
             if given is not None and tuple(given.shape) != (m, k):
                 raise ValueError(f"octex: output arrays must have shape {(m, k)}, not {tuple(given.shape)}")
-        res = _Resources(stream)
+        res = self._resources(stream)
         _lib.check(_lib.lib().octexB200Search(
             res.h, C.byref(p), self._h, C.c_void_p(ptrs[0]), C.c_int64(m), C.c_int64(d),
             C.c_void_p(ptrs[1]), C.c_void_p(ptrs[2]), C.c_int64(k), C.c_int32(1 if on_device else 0)))
         if on_device:
             res.sync()
+            _lib.check(_lib.lib().octexB200CheckLast(self._h))
         if neighbors is not None and neighbors is not I:
             neighbors[...] = I if not _is_torch(neighbors) or _is_torch(I) else torch.as_tensor(I)
             I = neighbors
@@ -323,7 +351,7 @@ class Index:
         """Search again the queries the previous ``search`` left on the GPU; results stay there.
         ``stream``: the CUDA stream (handle) the work is ordered after and signals back to."""
         p = search_params(**kw)
-        res = _Resources(stream)
+        res = self._resources(stream)
         _lib.check(_lib.lib().octexB200SearchResident(res.h, C.byref(p), self._h,
                                                       C.c_int64(n_queries), C.c_int64(k)))
 

@@ -43,13 +43,22 @@ class OracleTaps(C.Structure):
                 ("kept1_ids", C.c_void_p), ("kept1_dist", C.c_void_p), ("stats", C.c_void_p)]
 
 
+def reference_root() -> str:
+    """Where the reference's sources lie: $REFERENCE, else a checkout named ``reference`` beside
+    this repository (absent on most machines: then only the prebuilt _ref/ files are used)."""
+    given = os.environ.get("REFERENCE")
+    if given:
+        return given
+    return os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+
+
 def build(force: bool = False) -> str:
     """Compile the checker (and, when the reference sources are present, oracle/_ref)."""
     so = os.path.join(_HERE, "liboctex_oracle.so")
     src = [os.path.join(_HERE, f) for f in ("octex_oracle.cpp", "octex_oracle.h", "e8_port.hpp")]
     stale = not os.path.exists(so) or any(os.path.getmtime(s) > os.path.getmtime(so) for s in src)
     # where the reference sources are mounted, its own code compiled into _ref/ must be there too
-    reference = os.environ.get("REFERENCE", "/root/reference")
+    reference = reference_root()
     if os.path.exists(os.path.join(reference, "cpp/src/neighbors/octex/detail/search_kernels.cuh")):
         outs = ("libe8_ref.so", "libe8_ref_fma.so", "libe8_ref_cuda.so", "libref_search.so")
         shims = [os.path.join(_HERE, f) for f in ("ref_e8_shim.cpp", "ref_e8_cuda_shim.cu", "ref_search_shim.cu")]
@@ -58,7 +67,8 @@ def build(force: bool = False) -> str:
             if not os.path.exists(p) or any(os.path.getmtime(s) > os.path.getmtime(p) for s in shims):
                 stale = True
     if force or stale:
-        subprocess.check_call(["make", "-C", _HERE, "all"], stdout=subprocess.DEVNULL)
+        subprocess.check_call(["make", "-C", _HERE, "all", "REFERENCE=" + reference],
+                              stdout=subprocess.DEVNULL)
     return so
 
 
@@ -218,7 +228,8 @@ class _RefSearchArgs(C.Structure):
                 ("seg", C.c_void_p), ("w1", C.c_int32), ("cand1", C.c_void_p), ("dist1", C.c_void_p),
                 ("n1", C.c_void_p), ("kept1_ids", C.c_void_p), ("kept1_dist", C.c_void_p),
                 ("kept_ids", C.c_void_p), ("kept_dist", C.c_void_p),
-                ("best_ids", C.c_void_p), ("best_dist", C.c_void_p), ("kernel_ms", C.c_void_p)]
+                ("best_ids", C.c_void_p), ("best_dist", C.c_void_p), ("kernel_ms", C.c_void_p),
+                ("reps", C.c_int32), ("flush_mb", C.c_int32)]
 
 
 def ref_search():
@@ -228,15 +239,31 @@ def ref_search():
 
 
 def ref_search_pipeline(arrays, meta, y, qs, queries, k=10, *, read=32, starts=128, waves=2,
-                        rerank=128, wave_rerank=128, sketch_rank=False, final_rerank=32):
+                        rerank=128, wave_rerank=128, sketch_rank=False, final_rerank=32,
+                        reps=1, flush_mb=0):
     """Run the reference's probe / gather / rerank / pick-starts kernels on this machine's GPU on a
     batch whose projected coordinates ``y`` (fp16 bits), sketch-space queries ``qs`` and queries are
-    given.  Returns a dict: seg, cand1, dist1, n1, kept1_ids, kept1_dist, kept_ids, kept_dist, best_ids, best_dist (the
-    search result) and kernel_ms (device milliseconds of the first round's and of the waves' kernels)."""
+    given.  The index arrays may be numpy arrays or torch tensors already on the GPU.  Returns a
+    dict: seg, cand1, dist1, n1, kept1_ids, kept1_dist, kept_ids, kept_dist, best_ids, best_dist
+    (the search result) and kernel_ms (device milliseconds of the first round's and of the waves'
+    kernels: the median of ``reps`` runs, each stage starting after ``flush_mb`` MB were written to
+    push the index out of the L2 cache when that is not 0)."""
     lib_ = ref_search()
-    keep = {name: np.ascontiguousarray(arrays[name]) for name in
+
+    class _Held:  # a contiguous array or tensor with the address the C side reads
+        def __init__(self, x, as_u16=False):
+            if hasattr(x, "data_ptr"):
+                self.x = x.contiguous()
+                self.addr = self.x.data_ptr()
+            else:
+                self.x = np.ascontiguousarray(x)
+                if as_u16:
+                    self.x = self.x.view(np.uint16)
+                self.addr = self.x.ctypes.data
+            self.shape = tuple(self.x.shape)
+
+    keep = {name: _Held(arrays[name], name == "vectors") for name in
             ("lists", "keys", "offsets", "base", "sketch_scale", "sketch", "vectors", "table")}
-    keep["vectors"] = keep["vectors"].view(np.uint16)
     inv_f = np.asarray([np.float32(1.0 / float(f)) for f in meta["spacings"]], np.float32)
     y = np.ascontiguousarray(y, np.uint16)
     qs = np.ascontiguousarray(qs, np.float32)
@@ -261,7 +288,8 @@ def ref_search_pipeline(arrays, meta, y, qs, queries, k=10, *, read=32, starts=1
     for field, name in (("lists", "lists"), ("keys", "keys"), ("offsets", "offsets"), ("base", "base"),
                         ("scale", "sketch_scale"), ("sketch", "sketch"), ("vectors", "vectors"),
                         ("table", "table")):
-        setattr(a, field, keep[name].ctypes.data)
+        setattr(a, field, keep[name].addr)
+    a.reps, a.flush_mb = int(reps), int(flush_mb)
     a.m, a.y, a.qs, a.q = m, y.ctypes.data, qs.ctypes.data, q.ctypes.data
     a.read, a.starts, a.waves, a.rerank, a.wave_rerank, a.k = read, starts, waves, rerank, wave_rerank, k
     a.sketch_rank, a.final_rerank = int(sketch_rank), final_rerank

@@ -29,7 +29,7 @@ struct device_array {
   {
     err = cudaMalloc(&p, std::max<size_t>(bytes, 16));
     if (err == cudaSuccess && host != nullptr && copy && bytes != 0)
-      err = cudaMemcpy(p, host, bytes, cudaMemcpyHostToDevice);
+      err = cudaMemcpy(p, host, bytes, cudaMemcpyDefault);  // the source may be host or device memory
   }
   device_array(device_array const&) = delete;
   ~device_array() { cudaFree(p); }
@@ -94,6 +94,9 @@ struct ref_search_args {
   float* best_dist;
   float* kernel_ms;           // [2] (may be null): device time of the first round's kernels (lookup,
                               // gather, rerank) and of the waves' kernels, by CUDA events
+  int32_t reps;               // > 1: the two stages run this many times and kernel_ms holds the medians
+  int32_t flush_mb;           // > 0: a buffer of this many MB is overwritten before every timed stage,
+                              // so that the stage starts with none of the index in the L2 cache
 };
 
 // Returns 0, a CUDA error code, or -1 for arguments the kernels cannot take.
@@ -141,74 +144,98 @@ extern "C" int ref_search_pipeline(const ref_search_args* a)
   cudaEvent_t ev[4];
   for (auto& v : ev)
     cudaEventCreate(&v);
-  cudaEventRecord(ev[0]);
-  // cell lookup (search.cu:105-137)
-  {
-    const int64_t tot = int64_t{m} * C;
-    const unsigned grid = static_cast<unsigned>((tot + 255) / 256);
-    if (a->blocks == 4)
-      ref::probe_kernel<4><<<grid, 256>>>(y.as<__half>(), m, C, L, inv_f.as<float>(), offsets.as<int>(), T1,
-                                          keys.as<long long>(), a->mmax, base.as<int>(), a->list_len, lr,
-                                          a->log_buckets, seg.as<int2>());
-    else
-      ref::probe_kernel<2><<<grid, 256>>>(y.as<__half>(), m, C, L, inv_f.as<float>(), offsets.as<int>(), T1,
-                                          keys.as<long long>(), a->mmax, base.as<int>(), a->list_len, lr,
-                                          a->log_buckets, seg.as<int2>());
-  }
-  // first round: gather + sketch distances (search.cu:343-361), exact rerank into the kept list (:393)
+  const int reps = std::max(a->reps, 1);
+  device_array flush(nullptr, a->flush_mb > 0 ? static_cast<size_t>(a->flush_mb) << 20 : 16);
+  if (flush.err != cudaSuccess) return static_cast<int>(flush.err);
+  auto flush_l2 = [&] {
+    if (a->flush_mb > 0) cudaMemsetAsync(flush.p, 1, static_cast<size_t>(a->flush_mb) << 20);
+  };
   cudaFuncSetAttribute(ref::gather_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                        static_cast<int>(gather_smem(W, S, C)));
-  ref::gather_kernel<false><<<m, 256, gather_smem(W, S, C)>>>(
-    seg.as<int2>(), C, lists.as<int>(), a->stride, nullptr, 1, sketch.as<signed char>(), nullptr, 1,
-    scale.as<float>(), qs.as<float>(), S, W, logW, cand.as<int>(), dist.as<float>(), nin.as<int>());
-  if (a->sketch_rank)  // search.cu:384
-    ref::sketch_keep_kernel<<<m, 512>>>(cand.as<int>(), dist.as<float>(), nin.as<int>(), W, KO,
-                                        si.as<long long>(), sd.as<float>(), true);
-  else
-    ref::rerank_keep_kernel<<<m, 256, D * sizeof(float)>>>(cand.as<int>(), dist.as<float>(), nin.as<int>(), W,
-                                                           xptr.as<long long>(), a->n, D, q.as<float>(),
-                                                           a->rerank, KO, si.as<long long>(), sd.as<float>(),
-                                                           true);
-  cudaEventRecord(ev[1]);
-  cudaError_t e = cudaDeviceSynchronize();
-  if (e != cudaSuccess) return static_cast<int>(e);
-  cudaMemcpy(a->seg, seg.p, sizeof(int2) * m * C, cudaMemcpyDeviceToHost);
-  cudaMemcpy2D(a->cand1, sizeof(int) * a->w1, cand.p, sizeof(int) * W, sizeof(int) * W, m, cudaMemcpyDeviceToHost);
-  cudaMemcpy2D(a->dist1, sizeof(float) * a->w1, dist.p, sizeof(float) * W, sizeof(float) * W, m,
-               cudaMemcpyDeviceToHost);
-  cudaMemcpy(a->n1, nin.p, sizeof(int) * m, cudaMemcpyDeviceToHost);
-  cudaMemcpy(a->kept1_ids, si.p, sizeof(long long) * m * KO, cudaMemcpyDeviceToHost);
-  cudaMemcpy(a->kept1_dist, sd.p, sizeof(float) * m * KO, cudaMemcpyDeviceToHost);
-
-  // waves (search.cu:432-500): start points, their table rows, rerank into the kept list
-  if (a->waves > 0) {
+  if (a->waves > 0)
     cudaFuncSetAttribute(ref::gather_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          static_cast<int>(gather_smem(W2, S, a->starts)));
-    cudaEventRecord(ev[2]);
-    for (int wv = 0; wv < a->waves; wv++) {
-      ref::pick_starts_kernel<<<m, 256>>>(si.as<long long>(), KO, done.as<long long>(), a->starts * a->waves,
-                                          wv * a->starts, a->starts, a->table_len, seg2.as<int2>());
-      ref::gather_kernel<true><<<m, 512, gather_smem(W2, S, a->starts)>>>(
-        seg2.as<int2>(), a->starts, nullptr, a->table_len, tptr.as<long long>(), a->n, sketch.as<signed char>(),
-        nullptr, 1, scale.as<float>(), qs.as<float>(), S, W2, logW2, cand2.as<int>(), dist2.as<float>(),
-        n2.as<int>());
-      if (a->sketch_rank)  // search.cu:479
-        ref::sketch_keep_kernel<<<m, 512>>>(cand2.as<int>(), dist2.as<float>(), n2.as<int>(), W2, KO,
-                                            si.as<long long>(), sd.as<float>(), false);
+  std::vector<float> ms1, ms2;
+  cudaError_t e = cudaSuccess;
+  for (int rep = 0; rep < reps; rep++) {
+    flush_l2();
+    cudaEventRecord(ev[0]);
+    // cell lookup (search.cu:105-137)
+    {
+      const int64_t tot = int64_t{m} * C;
+      const unsigned grid = static_cast<unsigned>((tot + 255) / 256);
+      if (a->blocks == 4)
+        ref::probe_kernel<4><<<grid, 256>>>(y.as<__half>(), m, C, L, inv_f.as<float>(), offsets.as<int>(), T1,
+                                            keys.as<long long>(), a->mmax, base.as<int>(), a->list_len, lr,
+                                            a->log_buckets, seg.as<int2>());
       else
-        ref::rerank_keep_kernel<<<m, 256, D * sizeof(float)>>>(cand2.as<int>(), dist2.as<float>(), n2.as<int>(),
-                                                               W2, xptr.as<long long>(), a->n, D, q.as<float>(),
-                                                               a->wave_rerank, KO, si.as<long long>(),
-                                                               sd.as<float>(), false);
+        ref::probe_kernel<2><<<grid, 256>>>(y.as<__half>(), m, C, L, inv_f.as<float>(), offsets.as<int>(), T1,
+                                            keys.as<long long>(), a->mmax, base.as<int>(), a->list_len, lr,
+                                            a->log_buckets, seg.as<int2>());
     }
-    cudaEventRecord(ev[3]);
+    // first round: gather + sketch distances (search.cu:343-361), exact rerank into the kept list (:393)
+    ref::gather_kernel<false><<<m, 256, gather_smem(W, S, C)>>>(
+      seg.as<int2>(), C, lists.as<int>(), a->stride, nullptr, 1, sketch.as<signed char>(), nullptr, 1,
+      scale.as<float>(), qs.as<float>(), S, W, logW, cand.as<int>(), dist.as<float>(), nin.as<int>());
+    if (a->sketch_rank)  // search.cu:384
+      ref::sketch_keep_kernel<<<m, 512>>>(cand.as<int>(), dist.as<float>(), nin.as<int>(), W, KO,
+                                          si.as<long long>(), sd.as<float>(), true);
+    else
+      ref::rerank_keep_kernel<<<m, 256, D * sizeof(float)>>>(cand.as<int>(), dist.as<float>(), nin.as<int>(), W,
+                                                             xptr.as<long long>(), a->n, D, q.as<float>(),
+                                                             a->rerank, KO, si.as<long long>(), sd.as<float>(),
+                                                             true);
+    cudaEventRecord(ev[1]);
     e = cudaDeviceSynchronize();
     if (e != cudaSuccess) return static_cast<int>(e);
+    if (rep == reps - 1) {
+      cudaMemcpy(a->seg, seg.p, sizeof(int2) * m * C, cudaMemcpyDeviceToHost);
+      cudaMemcpy2D(a->cand1, sizeof(int) * a->w1, cand.p, sizeof(int) * W, sizeof(int) * W, m, cudaMemcpyDeviceToHost);
+      cudaMemcpy2D(a->dist1, sizeof(float) * a->w1, dist.p, sizeof(float) * W, sizeof(float) * W, m,
+                   cudaMemcpyDeviceToHost);
+      cudaMemcpy(a->n1, nin.p, sizeof(int) * m, cudaMemcpyDeviceToHost);
+      cudaMemcpy(a->kept1_ids, si.p, sizeof(long long) * m * KO, cudaMemcpyDeviceToHost);
+      cudaMemcpy(a->kept1_dist, sd.p, sizeof(float) * m * KO, cudaMemcpyDeviceToHost);
+    }
+    float t = 0.f;
+    cudaEventElapsedTime(&t, ev[0], ev[1]);
+    ms1.push_back(t);
+
+    // waves (search.cu:432-500): start points, their table rows, rerank into the kept list
+    if (a->waves > 0) {
+      flush_l2();
+      cudaEventRecord(ev[2]);
+      for (int wv = 0; wv < a->waves; wv++) {
+        ref::pick_starts_kernel<<<m, 256>>>(si.as<long long>(), KO, done.as<long long>(), a->starts * a->waves,
+                                            wv * a->starts, a->starts, a->table_len, seg2.as<int2>());
+        ref::gather_kernel<true><<<m, 512, gather_smem(W2, S, a->starts)>>>(
+          seg2.as<int2>(), a->starts, nullptr, a->table_len, tptr.as<long long>(), a->n, sketch.as<signed char>(),
+          nullptr, 1, scale.as<float>(), qs.as<float>(), S, W2, logW2, cand2.as<int>(), dist2.as<float>(),
+          n2.as<int>());
+        if (a->sketch_rank)  // search.cu:479
+          ref::sketch_keep_kernel<<<m, 512>>>(cand2.as<int>(), dist2.as<float>(), n2.as<int>(), W2, KO,
+                                              si.as<long long>(), sd.as<float>(), false);
+        else
+          ref::rerank_keep_kernel<<<m, 256, D * sizeof(float)>>>(cand2.as<int>(), dist2.as<float>(), n2.as<int>(),
+                                                                 W2, xptr.as<long long>(), a->n, D, q.as<float>(),
+                                                                 a->wave_rerank, KO, si.as<long long>(),
+                                                                 sd.as<float>(), false);
+      }
+      cudaEventRecord(ev[3]);
+      e = cudaDeviceSynchronize();
+      if (e != cudaSuccess) return static_cast<int>(e);
+      cudaEventElapsedTime(&t, ev[2], ev[3]);
+      ms2.push_back(t);
+    }
   }
   if (a->kernel_ms != nullptr) {
-    a->kernel_ms[0] = a->kernel_ms[1] = 0.f;
-    cudaEventElapsedTime(&a->kernel_ms[0], ev[0], ev[1]);
-    if (a->waves > 0) cudaEventElapsedTime(&a->kernel_ms[1], ev[2], ev[3]);
+    auto median = [](std::vector<float>& v) {
+      if (v.empty()) return 0.f;
+      std::sort(v.begin(), v.end());
+      return v[v.size() / 2];
+    };
+    a->kernel_ms[0] = median(ms1);
+    a->kernel_ms[1] = median(ms2);
   }
   for (auto& v : ev)
     cudaEventDestroy(v);

@@ -1,7 +1,8 @@
 """GPU parity: the CUDA path, called through the C interface, against the CPU checker on the same
 seeded inputs.  Integer and index work is compared bit for bit (cell codes, segments, candidate
 sets, ids); distances bit for bit too, because both sides sum in the same stated order.  The one
-tolerance is the tensor-core projection, compared with the ordered projection in test_gpu_project."""
+tolerance is the tensor-core projection, compared with the ordered projection in
+test_tensor_core_projection below."""
 import ctypes as C
 
 import numpy as np
@@ -247,6 +248,17 @@ def test_directory_load_equals_attach(oracle, small_index, gpu_small, tmp_path):
     want_i, want_d, _ = oracle.Index(cut, cmeta).search(queries, 10, read=8, starts=32, waves=1)
     assert np.array_equal(i2, want_i) and np.array_equal(d2.view(np.uint32), want_d.view(np.uint32))
     idx.close()
+    # saved parts (load.cu:252-270): two parts of four copies, the first three of each loaded
+    idx = octex_b200.load(path, placement="replicate", parts=2, copies_per_part=3)
+    assert idx.copies == 6
+    d2, i2 = idx.search(queries, 10, read=8, starts=32, waves=1)
+    sel = [0, 1, 2, 4, 5, 6]
+    cut = dict(arrays)
+    for name in ("lists", "keys", "offsets", "base", "proj", "shift"):
+        cut[name] = np.ascontiguousarray(arrays[name][sel])
+    want_i, want_d, _ = oracle.Index(cut, dict(meta, copies=6)).search(queries, 10, read=8, starts=32, waves=1)
+    assert np.array_equal(i2, want_i) and np.array_equal(d2.view(np.uint32), want_d.view(np.uint32))
+    idx.close()
     # host tiers (load.cu:328-330): arrays in page-locked host memory read through the same pointer;
     # same results, less device memory
     full_bytes = None
@@ -327,12 +339,10 @@ def test_dlpack_c_api(gpu_small):
     L.cuvsResourcesDestroy(res)
 
 
-def test_full_size_properties(oracle):
-    """Size-independent properties on a larger index built on the GPU (100 000 x 128, the plumbing
-    configuration with fewer copies): distances ascending, ids distinct and in range, every distance
-    equal to the exact fp32 distance to the stored fp16 row, recall against brute force, and the
-    neighbours the reference's own kernels find from the same projected coordinates."""
-    import torch
+@pytest.fixture(scope="module")
+def gpu_100k():
+    """100 000 x 128 rows (the plumbing configuration with fewer copies), built on the GPU:
+    (index, arrays on the device, meta, queries)."""
     from octex_b200 import build_index, synth
     base = synth.plumbing(100000, 128, seed=0)
     queries = synth.plumbing(1000, 128, seed=1)
@@ -340,6 +350,18 @@ def test_full_size_properties(oracle):
                                      log_buckets=16, table_len=32)
     arrays, meta = build_index.build_arrays(base, params, device="cuda", keep_on_device=True)
     idx = octex_b200.attach(arrays, meta, borrow=True)
+    yield idx, arrays, meta, queries
+    idx.close()
+
+
+def test_full_size_properties(oracle, gpu_100k):
+    """Size-independent properties on a larger index: distances ascending, ids distinct and in
+    range, every distance equal to the exact fp32 distance to the stored fp16 row, recall against
+    brute force, and the neighbours the reference's own kernels find from the same projected
+    coordinates."""
+    import torch
+    idx, arrays, meta, queries = gpu_100k
+    idx.set_debug(stats=False, taps=False)
     dist, ids = idx.search(queries, 10, read=32, starts=128, waves=3, rerank=256, wave_rerank=256)
     assert (np.diff(dist, axis=1) >= 0).all()
     assert ids.min() >= 0 and ids.max() < meta["n"]
@@ -368,7 +390,94 @@ def test_full_size_properties(oracle):
         assert agree >= 0.999
         same = ref["kept_ids"][:, :10] == ids
         np.testing.assert_allclose(ref["kept_dist"][:, :10][same], dist[same], rtol=1e-4, atol=1e-3)
+        idx.set_debug(taps=False)
+
+
+FUSED_SETS = [
+    dict(read=8, starts=32, waves=0),
+    dict(read=16, starts=32, waves=1, rerank=128, wave_rerank=384),
+    dict(read=8, starts=24, waves=2, rerank=64, wave_rerank=100),
+    dict(read=32, starts=128, waves=2, rerank=256, wave_rerank=256),
+    dict(read=8, starts=64, waves=1, sketch_rank=True, final_rerank=32),
+]
+
+
+def fused_against_inspected(oracle, idx, arrays, meta, queries):
+    """The search as it runs in production — the cells looked up inside the tensor-core
+    projection's epilogue, nothing kept for inspection — against the inspected run of the same
+    batch (codes written out, separate lookup kernel), which is compared with the CPU checker bit
+    for bit: segments, final kept lists, ids and distances must be identical.  The probe follows
+    the finest-level-first rule of cpp/tests/test_search.cu:86-170 of the reference."""
+    nq, C_ = len(queries), meta["copies"]
+    host = None
+    for kw in FUSED_SETS:
+        KO = max(kw["starts"], 10)
+        idx.set_projection(ordered=False)
+        idx.set_debug(stats=False, taps=True)
+        d_tap, i_tap = idx.search(queries, 10, **kw)
+        seg_tap = idx.fetch("seg", np.int32, (nq, C_, 2))
+        kept_tap = idx.fetch("kept_ids", np.int64, (nq, KO))
+        keptd_tap = idx.fetch("kept_dist", np.float32, (nq, KO))
+        y = idx.fetch("y", np.uint16, (nq, -1))
+        idx.set_debug(stats=False, taps=False)
+        d_run, i_run = idx.search(queries, 10, **kw)
+        with pytest.raises(ValueError, match="not kept"):
+            idx.fetch("y", np.uint16)  # nothing is kept for inspection on this path
+        seg_run = idx.fetch("seg", np.int32, (nq, C_, 2))
+        assert np.array_equal(seg_run, seg_tap), ("segments", kw)
+        assert np.array_equal(idx.fetch("kept_ids", np.int64, (nq, KO)), kept_tap), kw
+        assert np.array_equal(idx.fetch("kept_dist", np.float32, (nq, KO)).view(np.uint32),
+                              keptd_tap.view(np.uint32)), kw
+        assert np.array_equal(i_run, i_tap) and np.array_equal(d_run.view(np.uint32), d_tap.view(np.uint32)), kw
+        # and the inspected run is the checker's answer on the tensor-core coordinates
+        if host is None:
+            host = {k_: (v_.cpu().numpy() if hasattr(v_, "cpu") else v_) for k_, v_ in arrays.items()}
+        want_i, want_d, t = oracle.Index(host, meta).search(queries, 10, y_in=y, taps=("seg",), **kw)
+        assert np.array_equal(seg_run, t["seg"]), ("segments vs checker", kw)
+        assert np.array_equal(i_run, want_i), kw
+        assert np.array_equal(d_run.view(np.uint32), want_d.view(np.uint32)), kw
+    # with counters on: what the rounds read is the checker's count; of the levels the checker
+    # tries, the lookup skips those it knows to hold no cell at all
+    idx.set_debug(stats=True, taps=False)
+    kw = FUSED_SETS[1]
+    idx.search(queries, 10, **kw)
+    stats = idx.fetch("stats", np.int64, (nq, 8))
+    idx.set_debug(stats=True, taps=True)
+    idx.search(queries, 10, **kw)
+    y = idx.fetch("y", np.uint16, (nq, -1))
+    t = oracle.Index(host, meta).search(queries, 10, y_in=y, taps=("stats",), **kw)[2]
+    cols = [2, 3, 4, 5, 6]
+    assert np.array_equal(stats[:, cols], t["stats"][:, cols]), "per-query counters of the fused path"
+    assert (stats[:, 0] <= t["stats"][:, 0]).all() and (stats[:, 0] >= C_).all()
+    assert (stats[:, 1] >= stats[:, 0]).all()  # at least one table slot per level tried
+    idx.set_debug(stats=False, taps=False)
+
+
+def test_fused_lookup_path_wide(oracle, wide_index):
+    arrays, meta, _, queries = wide_index
+    idx = octex_b200.attach(arrays, meta, borrow=False)
+    fused_against_inspected(oracle, idx, arrays, meta, queries)
     idx.close()
+
+
+def test_fused_lookup_path_100k(oracle, gpu_100k):
+    idx, arrays, meta, queries = gpu_100k
+    fused_against_inspected(oracle, idx, arrays, meta, queries)
+
+
+def test_direct_launches_equal_graph(gpu_wide):
+    """use_graph = false (search.cu:885-920 of the reference: the same kernels launched directly)."""
+    idx, _, _, _, queries = gpu_wide
+    kw = dict(read=8, starts=32, waves=2, rerank=64, wave_rerank=64)
+    d0, i0 = idx.search(queries, 10, **kw)
+    p = octex_b200.search_params(use_graph=False, **kw)
+    I = np.zeros((len(queries), 10), np.int64)
+    D = np.zeros((len(queries), 10), np.float32)
+    _lib.check(_lib.lib().octexB200Search(C.c_size_t(0), C.byref(p), idx._h, C.c_void_p(queries.ctypes.data),
+                                          C.c_int64(len(queries)), C.c_int64(queries.shape[1]),
+                                          C.c_void_p(I.ctypes.data), C.c_void_p(D.ctypes.data),
+                                          C.c_int64(10), C.c_int32(0)))
+    assert np.array_equal(I, i0) and np.array_equal(D.view(np.uint32), d0.view(np.uint32))
 
 
 def test_tensor_core_projection(oracle, gpu_wide):

@@ -41,7 +41,13 @@ def worker(rank, world, port, path, out, placement, tiers):
     d, i = idx.search(q, 10, read=8, starts=32, waves=2, rerank=64, wave_rerank=64)
     res["dev_i"], res["dev_d"] = i.cpu().numpy(), d.cpu().numpy()
     np.savez(os.path.join(out, f"{placement}{rank}.npz"), **res)
-    dist.barrier()
+    rep = idx.memory_report()
+    assert rep["device"] == rank and rep["copies"] > 0 and rep["buffers"] > 0
+    # closing is a collective: a process that arrives late still finds its peers' memory mapped,
+    # and the early one does not free what the late one has mapped
+    if rank == 1:
+        import time
+        time.sleep(1.0)
     idx.close()
     dist.destroy_process_group()
 

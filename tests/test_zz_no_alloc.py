@@ -20,11 +20,14 @@ import pytest
 pytestmark = pytest.mark.gpu
 
 
-def static_codes(idx, meta, q_dev):
+def static_codes(idx, meta, q_dev, out=None):
+    """The call on torch's current stream; ``out`` (device int64 [m, copies, levels]) is made here
+    unless the caller brings it."""
     import torch
     from octex_b200 import _lib
     m = q_dev.shape[0]
-    out = torch.full((m, meta["copies"], len(meta["spacings"])), -7, dtype=torch.int64, device="cuda")
+    if out is None:
+        out = torch.full((m, meta["copies"], len(meta["spacings"])), -7, dtype=torch.int64, device="cuda")
     stream = torch.cuda.current_stream().cuda_stream
     rc = _lib.lib().octexB200QueryCodesStatic(idx._h, C.c_void_p(q_dev.data_ptr()), C.c_int64(m),
                                               C.c_void_p(out.data_ptr()), C.c_void_p(stream))
@@ -65,4 +68,42 @@ def test_static_scratch_matches_allocating_path(small_index):
     q_dev = torch.as_tensor(queries[:64], device="cuda")
     idx.search(q_dev, 10, read=8, starts=16, waves=0)
     assert np.array_equal(static_codes(idx, meta, q_dev), idx.fetch("codes", np.int64, (64, C_, L)))
+    idx.close()
+
+
+def test_static_scratch_on_a_four_block_index(wide_index):
+    """An index whose search projects on the tensor cores by default.  The static-scratch call
+    projects in dimension order, so its codes are those of the search under
+    ``set_projection(ordered=True)`` exactly, and those of the default search up to the few
+    coordinates the two summation orders round to neighbouring fp16 values.  The calls are made on
+    a stream of their own, and from the second call on the free device memory must not move: the
+    call allocates nothing."""
+    import torch
+    import octex_b200
+    arrays, meta, _, queries = wide_index
+    idx = octex_b200.attach(arrays, meta, borrow=False)
+    idx.set_debug(taps=True)
+    C_, L = meta["copies"], len(meta["spacings"])
+    q_dev = torch.as_tensor(queries, device="cuda")
+    nq = len(queries)
+    idx.set_projection(ordered=True)
+    idx.search(q_dev, 10, read=8, starts=16, waves=0)
+    want_ordered = idx.fetch("codes", np.int64, (nq, C_, L))
+    idx.set_projection(ordered=False)
+    idx.search(q_dev, 10, read=8, starts=16, waves=0)
+    codes_tc = idx.fetch("codes", np.int64, (nq, C_, L))
+    side = torch.cuda.Stream()
+    out = torch.empty((nq, C_, L), dtype=torch.int64, device="cuda")
+    torch.cuda.synchronize()
+    with torch.cuda.stream(side):
+        got = static_codes(idx, meta, q_dev, out)  # the first call on this GPU may load the module
+        free0 = torch.cuda.mem_get_info()[0]
+        for _ in range(3):
+            out.fill_(-7)
+            got = static_codes(idx, meta, q_dev, out)
+            assert torch.cuda.mem_get_info()[0] == free0, "a later call changed the free device memory"
+            assert np.array_equal(got, want_ordered)
+    differ = float((got != codes_tc).mean())
+    print(f"codes that differ from the tensor-core search's: {differ:.5f}")
+    assert differ <= 0.05
     idx.close()

@@ -50,10 +50,19 @@ WORKLOADS = {
         gen="embedding_like", n=1_000_000, dim=96, nq=10_000,
         build=dict(copies=64, blocks=4, pca_dims=64, list_len=32, min_cell=16, log_buckets=20,
                    sketch_width=64, table_len=64)),
+    # BASELINE.json config 1: the index at the reference's defaults
+    # (cpp/include/cuvs/neighbors/octex.hpp:32-92: 200 copies, lists of 64, 2^20 buckets, table of 64,
+    # sketch width chosen from the dimension) and its stated search parameters, not retuned
     "plumbing-100k": dict(
         gen="plumbing", n=100_000, dim=128, nq=1_000,
-        build=dict(copies=32, blocks=4, pca_dims=64, list_len=32, min_cell=1, log_buckets=16,
-                   sketch_width=64, table_len=32)),
+        build=dict(copies=200, blocks=4, pca_dims=64, list_len=64, min_cell=1, log_buckets=20,
+                   sketch_width=0, table_len=64),
+        search=dict(read=8, starts=32, waves=1, rerank=128, wave_rerank=128)),
+    # BASELINE.json config 3: 960-dimensional global-descriptor-like rows, 1 000 queries
+    "global-1m": dict(
+        gen="global_descriptor_like", n=1_000_000, dim=960, nq=1_000,
+        build=dict(copies=96, blocks=4, pca_dims=64, list_len=64, min_cell=16, log_buckets=20,
+                   sketch_width=128, table_len=64)),
 }
 LADDER = [
     dict(read=16, starts=32, waves=1, rerank=128, wave_rerank=384),
@@ -222,7 +231,8 @@ def algorithmic_bytes(stats, sp, meta, k):
     n1 = stats[:, 3]
     r1 = np.minimum(n1, sp["rerank"])  # the first round starts from an empty kept list
     waves = sp["waves"]
-    lists = (4 * stats[:, 2] + n1 * S + r1 * 2 * D + 4 * D + 4 * S + KO * 12).sum()
+    S4 = S + 4  # a sketch row of the first round: its codes and its fp32 constant
+    lists = (4 * stats[:, 2] + n1 * S4 + r1 * 2 * D + 4 * D + 4 * S + KO * 12).sum()
     pairs = len(stats) * meta["copies"]
     # the cell lookup happens inside the projection kernel: 16-byte table slots examined and the
     # segment written per (query, copy), next to the fp16 queries read
@@ -255,7 +265,7 @@ def run_reference(args, rank, world):
     dev = "cuda" if torch.cuda.is_available() else "cpu"
     arrays, meta = build_index.build_arrays(base, build_index.IndexParams(**w["build"]), device=dev)
     ox = oracle_py.Index(arrays, meta)
-    sp = given_search(args) if args.search else dict(LADDER[args.ladder_start])
+    sp = given_search(args) if args.search else dict(w.get("search", LADDER[args.ladder_start]))
     sample = queries[:args.cpu_sample]
     cores = os.cpu_count() or 1
     for _ in range(max(args.warmup, 1)):
@@ -452,7 +462,8 @@ def main():
     # search parameters: the cheapest rung of the ladder that reaches recall@10 >= 0.99
     chosen, rec = None, 0.0
     ids_run = dist_run = None
-    for sp in ([given_search(args)] if args.search else LADDER[args.ladder_start:]):
+    fixed = [given_search(args)] if args.search else ([dict(w["search"])] if "search" in w else None)
+    for sp in (fixed or LADDER[args.ladder_start:]):
         d_, i_ = idx.search(q_dev, K, **sp)
         r = recall_of(i_.cpu().numpy(), truth)
         log(f"[rank {rank}] {sp} recall@10 {r:.4f}")
@@ -592,8 +603,9 @@ def main():
                                  "frac": alg[k_] / (kernel_ms[k_] * 1e-3) / 1e9 / peak} for k_ in timed}}
     if sharded:
         roofline["kernel_ms_slowest_rank"] = kernel_ms_max
-        roofline["note"] = ("round_rows here = exchange of the kept lists (NCCL send / receive) + merge + "
-                            "the wave of this GPU's slice; best_k includes the gathering of the results")
+        roofline["note"] = ("exchange = the kept lists of the first round to the GPUs that own the queries "
+                            "(NCCL send / receive), merge = their merge; round_rows = the wave of this "
+                            "GPU's slice of the batch; gather_results = all-gather of the results")
     config = workload_config(args, w, sp, world)
     config.update({"recall_at_10": rec, "recall_at_10_e2e": rec_e2e, "e2e_ids_equal_resident": e2e_same,
                    "index_bytes": index_bytes, "l2": "flushed between timed steps (256 MB fill)",

@@ -246,8 +246,9 @@ OCTEX_B200_EXPORT cuvsError_t octexB200SearchResident(cuvsResources_t res,
 
 /* detail::timed_batch (search.cu:965-981) per kernel: one batch of the queries already on the GPU,
  * launched kernel by kernel with events between them. ms receives the milliseconds of centre +
- * sketch query, projection, cell codes, cell lookup, first round, each wave, best k; *count their
- * number. */
+ * sketch query, projection, cell codes, cell lookup, first round, (several processes, shard
+ * placement: exchange of the kept lists, their merge,) each wave, best k (several processes: the
+ * gathering of the results); *count their number. */
 OCTEX_B200_EXPORT cuvsError_t octexB200ProfileBatch(cuvsResources_t res,
                                                     cuvsOctexSearchParams_t params,
                                                     cuvsOctexIndex_t index, int64_t n_queries,

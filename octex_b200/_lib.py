@@ -8,7 +8,8 @@ import ctypes as C
 import os
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "lib", "liboctex_b200.so")
+#: the library built in-tree; OCTEX_B200_LIB names another build of it (a debug or experimental one)
+LIB_PATH = os.environ.get("OCTEX_B200_LIB") or os.path.join(_PKG, "lib", "liboctex_b200.so")
 CUVS_ERROR, CUVS_SUCCESS = 0, 1
 _lib = None
 

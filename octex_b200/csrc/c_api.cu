@@ -439,7 +439,7 @@ cuvsError_t octexB200MemoryReport(cuvsOctexIndex_t index, int64_t* bytes)
     auto dev = [](octex_b200::dbuf const& b) { return b.host ? int64_t{0} : static_cast<int64_t>(b.size); };
     bytes[0] = p.device;
     bytes[1] = dev(p.lists) + dev(p.base) + dev(p.cell_table) + dev(p.cell_off) + dev(p.cell_mask) + dev(p.level_on);
-    bytes[2] = dev(p.sketch);
+    bytes[2] = dev(p.sketch) + dev(p.sketch_norm);
     bytes[3] = dev(p.table);
     bytes[4] = dev(p.vectors);
     bytes[5] = dev(p.ut) + dev(p.shift) + dev(p.inv_f) + dev(p.mean) + dev(p.basis) + dev(p.scale) +

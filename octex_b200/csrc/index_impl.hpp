@@ -18,6 +18,8 @@
 //   basis   f32 [dim, S]         scale f32 [S]     sketch i8 [n, S]
 //   vectors f16 [n, dim]         table i32 [n, table_len]
 // * level_on u8 [Cg, L]          1 when the level of the copy holds at least one cell
+// * sketch_norm f32 [n]          sum_k (code_k scale_k)^2 of every sketch row, computed at placement
+//                                (the row's constant in the integer form of the sketch distance)
 #pragma once
 
 #include "comm.hpp"
@@ -65,6 +67,7 @@ struct device_part {
   int ldu        = 0;
   dbuf lists, base, ut, shift, inv_f, mean, basis, scale, sketch, vectors, table, level_on;
   dbuf cell_table, cell_off, cell_mask;  // open-addressing table of the cells of every (copy, level)
+  dbuf sketch_norm;                      // f32 [n]: sum_k (code_k scale_k)^2 of every sketch row
   dealt_rows table_rows, sketch_rows, vector_rows;
   cudaStream_t stream = nullptr;
   int64_t bytes       = 0;

@@ -107,6 +107,12 @@ void probe(const long long* codes, int m, int C, int L, const cell_slot* table, 
            const int* tmask, const int* base, const unsigned char* level_on, int list_len, int lr,
            int2* seg, long long* stats, cudaStream_t s);
 
+/// norm [rows] = sum_k (code_k * scale_k)^2 of each row of codes [rows, S] as fp32 (one fused
+/// multiply-add per code, in code order): the part of the sketch distance that depends on the row
+/// alone. All device memory.
+void sketch_row_norms(const signed char* codes, const float* scale, int64_t rows, int S, float* norm,
+                      cudaStream_t s);
+
 /// Where the rows of an array live when they are dealt over the GPUs in ranges of `rows`
 /// (ptrs[g] = start of rows [g * rows, (g + 1) * rows) in that GPU's memory, mapped into this
 /// process); ptrs == nullptr: the whole array is behind the plain pointer. The reference's
@@ -134,8 +140,10 @@ struct round_args {
   int done_stride = 0;
   int done_off = 0;  // entries of earlier waves
   int pick_slots = 0;  // hash slots for the earlier start points (power of two)
-  // sketch
+  // sketch: rows of sw codes; sketch_norm [n]: the constant of every row (sketch_row_norms),
+  // whole on every GPU even when the rows are dealt
   const signed char* sketch = nullptr;
+  const float* sketch_norm = nullptr;
   const float* scale = nullptr;
   const float* qs = nullptr;  // [m, sw]
   int sw = 0;
@@ -153,6 +161,8 @@ struct round_args {
   int ht_slots = 0;   // ints of the hash set region (>= largest set used, >= pick_slots)
   int cap_slots = 0;  // largest gather hash set (slots)
   int hash_twelfths = 16;  // slots per 12 gathered entries (host: as sparse as shared memory allows)
+  int keep_sketch = 0;  // the sketch and its row constants fit the L2 cache with room to spare: load them
+                        // with an evict-last policy, the large arrays with evict-first (host decides)
   int threads = kRoundThreads;  // threads per query block: 128, 256 or 512 (host: the smallest
                                 // that still fills a multiprocessor with the blocks that fit it)
   int nmax = 0;       // capacity of the candidate / distance arrays

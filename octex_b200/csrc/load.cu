@@ -317,6 +317,20 @@ void place(index_impl& ix, source_arrays const& src)
     put_rows_dealt(p.sketch, p.sketch_rows, a.sketch, static_cast<size_t>(S));
   else
     put_rows(p.sketch, a.sketch, static_cast<size_t>(N * S));
+  // The constant of every sketch row (kernels::sketch_row_norms), 4 bytes per row, on this GPU for
+  // all rows whatever tier or process holds the codes: the rows pass through the GPU in chunks.
+  {
+    own(p.sketch_norm, static_cast<size_t>(N) * sizeof(float));
+    const int64_t chunk = std::max<int64_t>(1, (int64_t{256} << 20) / S);
+    dbuf raw(p.device, static_cast<size_t>(std::min(chunk, N) * S));
+    for (int64_t r = 0; r < N; r += chunk) {
+      const int64_t nr = std::min(chunk, N - r);
+      st.copy(raw.ptr, a.sketch + r * S, static_cast<size_t>(nr * S));
+      kernels::sketch_row_norms(raw.as<signed char>(), p.scale.as<float>(), nr, static_cast<int>(S),
+                                p.sketch_norm.as<float>() + r, p.stream);
+      OCTEX_CUDA_TRY(cudaStreamSynchronize(p.stream));  // raw is reused
+    }
+  }
   if (params.vectors_on_host)
     put_rows_host(p.vectors, a.vectors, static_cast<size_t>(N * D) * sizeof(__half));
   else if (params.shard_vectors && many)

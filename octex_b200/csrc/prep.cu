@@ -327,6 +327,32 @@ __global__ void probe_kernel(const long long* __restrict__ codes,
   }
 }
 
+// The part of the sketch distance that depends on the row alone. The reference scores
+// sum_k (c_k s_k - q_k)^2 in fp32 per candidate (search_kernels.cuh:228-251); expanded,
+// sum_k (c_k s_k)^2 is a constant of the row and is computed here once, when the index is placed.
+__global__ void sketch_row_norms_kernel(const signed char* __restrict__ codes,
+                                        const float* __restrict__ scale,
+                                        int64_t rows,
+                                        int S,
+                                        float* __restrict__ norm)
+{
+  const int64_t r = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (r >= rows) return;
+  const uint4* src = reinterpret_cast<const uint4*>(codes + r * S);
+  float acc        = 0.f;
+  for (int c = 0; c < S / 16; c++) {
+    const uint4 v        = src[c];
+    const unsigned wd[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int t = 0; t < 16; t++) {
+      const int code = static_cast<signed char>((wd[t >> 2] >> (8 * (t & 3))) & 0xffu);
+      const float x  = __fmul_rn(static_cast<float>(code), scale[c * 16 + t]);
+      acc            = __fmaf_rn(x, x, acc);
+    }
+  }
+  norm[r] = acc;
+}
+
 // search_kernels.cuh:672-685
 __global__ void take_k_kernel(const long long* __restrict__ si,
                               const float* __restrict__ sd,
@@ -425,6 +451,13 @@ void probe(const long long* codes, int m, int C, int L, const cell_slot* table, 
   if (pairs <= 0) return;
   probe_kernel<<<blocks_for(pairs, 256), 256, 0, s>>>(codes, pairs, C, L, table, toff, tmask, base, level_on,
                                                       list_len, lr, seg, stats);
+}
+
+void sketch_row_norms(const signed char* codes, const float* scale, int64_t rows, int S, float* norm,
+                      cudaStream_t s)
+{
+  if (rows <= 0) return;
+  sketch_row_norms_kernel<<<blocks_for(rows, 128), 128, 0, s>>>(codes, scale, rows, S, norm);
 }
 
 void take_k(const long long* si, const float* sd, int KO, int k, int m, long long* bi, float* bd,

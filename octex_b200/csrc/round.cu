@@ -51,6 +51,8 @@ struct round_layout {
     sorted = cand + pool_words;
     sid    = take(rm);
     sdv    = take(rm);
+    // first round: 16-bit weights of the integer sketch distance (two per word) and its per-query
+    // constants (-2 alpha, sum of q^2); waves: the sketch-space query and the scales as floats
     qv     = take(a.sw);
     sc     = take(a.sw);
     fq     = take(a.D);
@@ -131,40 +133,6 @@ __device__ __forceinline__ void bitonic_sort(unsigned long long* key, int P)
   }
 }
 
-/// Ascending sort of 64 keys in shared memory by one warp (the caller's warp 0), two keys per lane
-/// in registers: element e = lane + 32 r. The same network as bitonic_sort, without block barriers.
-/// The other warps wait at the caller's next barrier.
-__device__ __forceinline__ void warp_sort64(unsigned long long* key)
-{
-  const int lane = threadIdx.x & 31;
-  unsigned long long k[2] = {key[lane], key[lane + 32]};
-#pragma unroll
-  for (int size = 2; size <= 64; size <<= 1) {
-#pragma unroll
-    for (int stride = size >> 1; stride > 0; stride >>= 1) {
-      if (stride == 32) {
-        // partners sit in the same lane; size is 64 here, so the order is ascending
-        const unsigned long long lo = k[0] < k[1] ? k[0] : k[1], hi = k[0] < k[1] ? k[1] : k[0];
-        k[0] = lo;
-        k[1] = hi;
-      } else {
-#pragma unroll
-        for (int r = 0; r < 2; r++) {
-          const int e                  = lane + 32 * r;
-          const unsigned long long o   = __shfl_xor_sync(0xffffffffu, k[r], stride);
-          const bool up                = (e & size) == 0;
-          const bool lower             = (lane & stride) == 0;  // this lane holds the lower index of the pair
-          const bool take_min          = up == lower;
-          const unsigned long long mn  = k[r] < o ? k[r] : o, mx = k[r] < o ? o : k[r];
-          k[r] = take_min ? mn : mx;
-        }
-      }
-    }
-  }
-  key[lane]      = k[0];
-  key[lane + 32] = k[1];
-}
-
 struct radix_cut_t {
   unsigned long long prefix, mask;
 };
@@ -215,19 +183,20 @@ __device__ __forceinline__ radix_cut_t radix_cut(HiAt hi_at, LoAt lo_at, int n, 
       }
       const unsigned before = inc - mine;
       if (before < static_cast<unsigned>(need) && inc >= static_cast<unsigned>(need)) {
-        unsigned cum = before;
+        unsigned cum = before, size = h[7];
         int d        = 7;
 #pragma unroll
         for (int t = 0; t < 8; t++) {
           if (cum + h[t] >= static_cast<unsigned>(need)) {
-            d = t;
+            d    = t;
+            size = h[t];
             break;
           }
           cum += h[t];
         }
         ctrl[1] = 8 * lane + d;                  // digit
         ctrl[2] = need - static_cast<int>(cum);  // still needed from that bucket
-        ctrl[3] = static_cast<int>(h[d]);        // bucket size
+        ctrl[3] = static_cast<int>(size);        // bucket size
       }
     }
     __syncthreads();
@@ -247,33 +216,134 @@ __device__ __forceinline__ radix_cut_t radix_cut(HiAt hi_at, LoAt lo_at, int n, 
                      (static_cast<unsigned long long>(mask_hi) << 32) | mask_lo};
 }
 
+/// The same threshold as radix_cut with, in the usual case, one counting pass instead of three or
+/// four: the high words (distances of one query: a narrow range of bit patterns) are binned over
+/// their own range [min, max] into 256 bins, the bin that holds the R-th key is found, and the
+/// R-th key itself is ranked among the few members of that bin. Falls back on radix_cut when that
+/// bin holds more than 128 keys (many equal or nearly equal distances). hist: 256 words, used as
+/// counters and then as the list of the bin's members; ctrl[1], [2], [3], [7] are used.
+template <typename HiAt, typename LoAt>
+__device__ __forceinline__ radix_cut_t smallest_cut(HiAt hi_at, LoAt lo_at, int n, int R, unsigned* hist,
+                                                    int* ctrl)
+{
+  constexpr int kSide = 128;
+  const int lane = threadIdx.x & 31;
+  unsigned* uc   = reinterpret_cast<unsigned*>(ctrl);
+  for (int i = threadIdx.x; i < 256; i += blockDim.x)
+    hist[i] = 0;
+  if (threadIdx.x == 0) {
+    uc[1] = ~0u;
+    uc[2] = 0u;
+    uc[7] = 0u;
+  }
+  __syncthreads();
+  unsigned lo = ~0u, hi = 0u;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const unsigned h = hi_at(i);
+    lo               = min(lo, h);
+    hi               = max(hi, h);
+  }
+  lo = __reduce_min_sync(0xffffffffu, lo);
+  hi = __reduce_max_sync(0xffffffffu, hi);
+  if (lane == 0) {
+    atomicMin(&uc[1], lo);
+    atomicMax(&uc[2], hi);
+  }
+  __syncthreads();
+  lo           = uc[1];
+  hi           = uc[2];
+  const int sh = max(0, 24 - __clz(static_cast<int>(hi - lo)));  // (hi - lo) >> sh < 256
+  for (int i = threadIdx.x; i < n; i += blockDim.x)
+    atomicAdd(&hist[(hi_at(i) - lo) >> sh], 1u);
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    // lane l owns bins 8l .. 8l+7: the bin at which the running count reaches R
+    unsigned h[8], mine = 0;
+#pragma unroll
+    for (int t = 0; t < 8; t++) {
+      h[t] = hist[8 * lane + t];
+      mine += h[t];
+    }
+    unsigned inc = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const unsigned u = __shfl_up_sync(0xffffffffu, inc, o);
+      if (lane >= o) inc += u;
+    }
+    const unsigned before = inc - mine;
+    if (before < static_cast<unsigned>(R) && inc >= static_cast<unsigned>(R)) {
+      unsigned cum = before, size = h[7];
+      int d        = 7;
+#pragma unroll
+      for (int t = 0; t < 8; t++) {
+        if (cum + h[t] >= static_cast<unsigned>(R)) {
+          d    = t;
+          size = h[t];
+          break;
+        }
+        cum += h[t];
+      }
+      ctrl[1] = 8 * lane + d;               // bin
+      ctrl[2] = R - static_cast<int>(cum);  // still needed from that bin
+      ctrl[3] = static_cast<int>(size);     // its size
+    }
+  }
+  __syncthreads();
+  const unsigned bin = static_cast<unsigned>(ctrl[1]);
+  const int left = ctrl[2], bucket = ctrl[3];
+  if (bucket == left) {
+    // the bin is taken whole: every key whose high word is below the next bin's first value
+    unsigned long long top = static_cast<unsigned long long>(lo) + ((static_cast<unsigned long long>(bin) + 1) << sh) - 1;
+    if (top > 0xffffffffULL) top = 0xffffffffULL;
+    __syncthreads();
+    return radix_cut_t{(top << 32) | 0xffffffffULL, ~0ULL};
+  }
+  if (bucket > kSide) {
+    __syncthreads();
+    return radix_cut(hi_at, lo_at, n, R, hist, ctrl);
+  }
+  unsigned long long* side = reinterpret_cast<unsigned long long*>(hist);  // the counters are dead
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const unsigned h = hi_at(i);
+    if (((h - lo) >> sh) == bin) side[atomicAdd(&uc[7], 1u)] = (static_cast<unsigned long long>(h) << 32) | lo_at(i);
+  }
+  __syncthreads();
+  if (threadIdx.x < bucket) {
+    const unsigned long long mine = side[threadIdx.x];
+    int below                     = 0;
+    for (int j = 0; j < bucket; j++)
+      below += side[j] < mine;
+    if (below == left - 1) {  // the left-th smallest of the bin is the R-th smallest of all
+      uc[2] = static_cast<unsigned>(mine >> 32);
+      uc[3] = static_cast<unsigned>(mine);
+    }
+  }
+  __syncthreads();
+  const unsigned long long cut = (static_cast<unsigned long long>(uc[2]) << 32) | uc[3];
+  __syncthreads();
+  return radix_cut_t{cut, ~0ULL};
+}
+
+/// Ascending order of cnt <= blockDim.x distinct keys src[0, cnt) into dst (another array): a
+/// thread counts the keys below its own and puts it there. No step depends on another, which
+/// suits the short lists a merge usually sorts better than a sorting network run by one warp.
+__device__ __forceinline__ void rank_sort(const unsigned long long* src, int cnt, unsigned long long* dst)
+{
+  if (threadIdx.x < cnt) {
+    const unsigned long long mine = src[threadIdx.x];
+    int below                     = 0;
+    for (int j = 0; j < cnt; j++)
+      below += src[j] < mine;
+    dst[below] = mine;
+  }
+}
+
 /// float(h) - q for an fp16 bit pattern h: the mixed-precision subtract of sm_100 (PTX ISA 8.6),
 /// the same value as converting first (the conversion is exact) without the conversion.
 __device__ __forceinline__ float half_minus(unsigned short h, float q)
 {
   float d;
   asm("sub.rn.f32.f16 %0, %1, %2;" : "=f"(d) : "h"(h), "f"(q));
-  return d;
-}
-
-/// Eight int8 codes (two 32-bit words) against eight (scale, query) pairs: sum of
-/// (code * scale - q)^2 with two fused multiply-adds per code, in code order. The int8 -> float
-/// conversion: one byte permute makes the fp16 patterns 0x64bb = 1024 + (code + 128) of two codes,
-/// and the mixed-precision subtract of 1152 gives each code exactly, off the conversion pipe.
-__device__ __forceinline__ float sketch_chunk8(uint2 w, const float* s, const float* q)
-{
-  const unsigned x0 = w.x ^ 0x80808080u, x1 = w.y ^ 0x80808080u;  // code + 128 in every byte
-  float d           = 0.f;
-#pragma unroll
-  for (int p = 0; p < 4; p++) {
-    const unsigned hh = __byte_perm(p < 2 ? x0 : x1, 0x64646464u, (p & 1) ? 0x4342 : 0x4140);
-    const float c0    = half_minus(static_cast<unsigned short>(hh & 0xffffu), 1152.0f);
-    const float c1    = half_minus(static_cast<unsigned short>(hh >> 16), 1152.0f);
-    const float t0    = __fmaf_rn(c0, s[2 * p], -q[2 * p]);
-    d                 = __fmaf_rn(t0, t0, d);
-    const float t1    = __fmaf_rn(c1, s[2 * p + 1], -q[2 * p + 1]);
-    d                 = __fmaf_rn(t1, t1, d);
-  }
   return d;
 }
 
@@ -298,71 +368,200 @@ __device__ __forceinline__ bool may_prefetch(const row_map& m)
   return !kDealt || m.ptrs == nullptr;
 }
 
-/// Sketch distances of the candidates cand[0, n) into dist[0, n) for a sketch of at most 32 chunks
-/// of eight codes: kLw (a power of two >= chunks) lanes own a row, one chunk each with its scale
-/// and query coordinates in registers; the chunk sums of a row are added by a butterfly over its
-/// lanes (strides 1, 2, 4, ...); a lane group has four rows in flight. Straight-line code: a lane
-/// past the last row or past the last chunk works on a valid stand-in and its result is dropped
-/// (a chunk past the end has scale and query 0, so it adds exactly 0).
-/// kFull: the sketch is exactly 8 * kLw codes wide (a power of two), a compile-time width.
-template <int kLw, bool kDealt, bool kFull = false>
-__device__ __forceinline__ void sketch_rows(const int* cand, int n, const signed char* __restrict__ sketch,
-                                            const row_map& map, int Srt, const float* sc, const float* qv,
-                                            float* dist)
+/// The query's side of the sketch distance, made once per query block by its first warp.
+/// The reference scores sum_k (c_k s_k - q_k)^2 in fp32 per candidate (search_kernels.cuh:228-251).
+/// Expanded: sum_k (c_k s_k)^2 - 2 sum_k c_k (s_k q_k) + sum_k q_k^2. The first sum is a constant
+/// of the row, computed when the index is placed (norm [n]); the last is a constant of the
+/// query; the middle one becomes an exact integer dot product of the int8 codes with 16-bit weights
+/// w_k = rint(s_k q_k / alpha), alpha = max_k |s_k q_k| / 32000 (two codes per dp2a). The value
+/// differs from the fp32 sum by the rounding of the weights (at most 1.6e-5 of the largest product
+/// per term) and of three fp32 operations. Every operation and its order are stated here and in
+/// the CPU checker, which evaluates the same form.
+/// Writes w16 [S / 2] (weights of codes 2i and 2i + 1 in the low and high half of word i) and
+/// kq[0] = -2 alpha, kq[1] = sum_k q_k^2 (partial sum k mod 32, butterfly with strides 1 .. 16).
+__device__ __forceinline__ void sketch_query_setup(const float* __restrict__ qs, const float* __restrict__ scale,
+                                                   int S, int* w16, float* kq)
+{
+  const int lane = threadIdx.x & 31;
+  float amax = 0.f, qq = 0.f;
+  for (int k = lane; k < S; k += 32) {
+    const float q = qs[k];
+    amax          = fmaxf(amax, fabsf(__fmul_rn(scale[k], q)));
+    qq            = __fmaf_rn(q, q, qq);
+  }
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    qq   = __fadd_rn(qq, __shfl_xor_sync(0xffffffffu, qq, o));
+  }
+  const float alpha = (amax > 0.f && amax <= FLT_MAX) ? __fdiv_rn(amax, 32000.0f) : 1.0f;
+  short* w = reinterpret_cast<short*>(w16);
+  for (int k = lane; k < S; k += 32) {
+    const float r = rintf(__fdiv_rn(__fmul_rn(scale[k], qs[k]), alpha));
+    w[k]          = static_cast<short>(r != r ? 0 : static_cast<int>(fminf(fmaxf(r, -32000.0f), 32000.0f)));
+  }
+  if (lane == 0) {
+    kq[0] = -2.0f * alpha;
+    kq[1] = qq;
+  }
+}
+
+/// Sketch distances of the candidates cand[0, n) into dist[0, n): kLw (a power of two >= S / 16)
+/// lanes own a row, sixteen codes (one 16-byte load) and their eight weight pairs each; a lane's
+/// dot product takes eight dp2a; the lanes of a row add theirs by a butterfly; four rows per lane
+/// group are in flight. A lane past the last row works on the last row and a lane past the last
+/// chunk on chunk 0 with zero weights; their results are dropped or add 0.
+// ---- L2 residency ---------------------------------------------------------------------------------
+//
+// The int8 sketch and its row constants are the arrays every query reads most often (hundreds of
+// rows per round) and, for an index of a million rows, small enough to stay in the 126 MB L2 cache
+// next to everything else; the fp16 vectors, the lists and the neighbor table are read once or a
+// few times per batch and are many times larger. When the host finds that the sketch fits, the
+// kernels load sketch rows and constants with an evict-last policy and the large arrays with an
+// evict-first policy, so that the streaming reads do not push the sketch out.
+
+__device__ __forceinline__ unsigned long long l2_policy_keep()
+{
+  unsigned long long p;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+
+__device__ __forceinline__ unsigned long long l2_policy_stream()
+{
+  unsigned long long p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+
+__device__ __forceinline__ uint4 ldg16_hint(const void* a, unsigned long long policy)
+{
+  uint4 v;
+  asm volatile("ld.global.nc.L2::cache_hint.v4.u32 {%0, %1, %2, %3}, [%4], %5;"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(a), "l"(policy));
+  return v;
+}
+
+__device__ __forceinline__ float ldg_f32_hint(const float* a, unsigned long long policy)
+{
+  float v;
+  asm volatile("ld.global.nc.L2::cache_hint.f32 %0, [%1], %2;" : "=f"(v) : "l"(a), "l"(policy));
+  return v;
+}
+
+__device__ __forceinline__ int ldg_i32_hint(const int* a, unsigned long long policy)
+{
+  int v;
+  asm volatile("ld.global.nc.L2::cache_hint.s32 %0, [%1], %2;" : "=r"(v) : "l"(a), "l"(policy));
+  return v;
+}
+
+template <int kLw, bool kDealt>
+__device__ __forceinline__ void sketch_rows_int(const int* cand, int n, const signed char* __restrict__ sketch,
+                                                const float* __restrict__ norm, const row_map& map, int S,
+                                                const int* w16, const float* kq, float* dist, bool keep)
 {
   constexpr int kG = 32 / kLw;  // rows per warp and step
+  constexpr int kU = 4;          // rows of a lane group in flight
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   const int sub = lane % kLw, grp = lane / kLw;
-  const int S      = kFull ? 8 * kLw : Srt;
-  const int chunks = S / 8;
-  const bool live  = sub < chunks;
+  const bool live  = 16 * sub < S;
   const int subc   = live ? sub : 0;
-  float cs[8], cq[8];
+  int w[8];
+  {
+    const int4 w0 = reinterpret_cast<const int4*>(w16)[2 * subc];
+    const int4 w1 = reinterpret_cast<const int4*>(w16)[2 * subc + 1];
+    w[0] = w0.x, w[1] = w0.y, w[2] = w0.z, w[3] = w0.w, w[4] = w1.x, w[5] = w1.y, w[6] = w1.z, w[7] = w1.w;
 #pragma unroll
-  for (int b = 0; b < 8; b++) {
-    cs[b] = live ? sc[sub * 8 + b] : 0.f;
-    cq[b] = live ? qv[sub * 8 + b] : 0.f;
+    for (int b = 0; b < 8; b++)
+      if (!live) w[b] = 0;
   }
+  const float beta = kq[0], qq = kq[1];
+  const unsigned long long pol = l2_policy_keep();
   const int rpp = nw * kG;  // rows per step of the block
-  for (int jb = 0; jb < n; jb += 4 * rpp) {
-    uint2 w[4];
-    int j[4];
+  for (int jb = 0; jb < n; jb += kU * rpp) {
+    uint4 c[kU];
+    float nrm[kU];
+    int j[kU];
 #pragma unroll
-    for (int u = 0; u < 4; u++) {
-      j[u]         = jb + u * rpp + warp * kG + grp;
-      const int id = cand[min(j[u], n - 1)];
-      w[u] = __ldg(reinterpret_cast<const uint2*>(row_of<kDealt>(sketch, map, id, S)) + subc);
+    for (int u = 0; u < kU; u++) {
+      j[u]            = jb + u * rpp + warp * kG + grp;
+      const int id    = cand[min(j[u], n - 1)];
+      const uint4* row = reinterpret_cast<const uint4*>(row_of<kDealt>(sketch, map, id, S)) + subc;
+      if (keep) {
+        c[u]   = ldg16_hint(row, pol);
+        nrm[u] = ldg_f32_hint(norm + id, pol);
+      } else {
+        c[u]   = __ldg(row);
+        nrm[u] = __ldg(norm + id);
+      }
     }
 #pragma unroll
-    for (int u = 0; u < 4; u++) {
-      float d = sketch_chunk8(w[u], cs, cq);
+    for (int u = 0; u < kU; u++) {
+      int d = __dp2a_lo(w[0], static_cast<int>(c[u].x), 0);
+      d     = __dp2a_hi(w[1], static_cast<int>(c[u].x), d);
+      d     = __dp2a_lo(w[2], static_cast<int>(c[u].y), d);
+      d     = __dp2a_hi(w[3], static_cast<int>(c[u].y), d);
+      d     = __dp2a_lo(w[4], static_cast<int>(c[u].z), d);
+      d     = __dp2a_hi(w[5], static_cast<int>(c[u].z), d);
+      d     = __dp2a_lo(w[6], static_cast<int>(c[u].w), d);
+      d     = __dp2a_hi(w[7], static_cast<int>(c[u].w), d);
 #pragma unroll
       for (int o = 1; o < kLw; o <<= 1)
-        d = __fadd_rn(d, __shfl_xor_sync(0xffffffffu, d, o));
-      if (j[u] < n && sub == 0) dist[j[u]] = d;
+        d += __shfl_xor_sync(0xffffffffu, d, o);
+      if (j[u] < n && sub == 0)
+        dist[j[u]] = fmaxf(__fadd_rn(nrm[u], __fmaf_rn(beta, static_cast<float>(d), qq)), 0.f);
     }
   }
 }
 
-/// As sketch_rows for a sketch of exactly 16 * kLw codes, a lane scoring two neighbouring 8-code
-/// chunks of a row (one 16-byte load): the two chunk sums are added in the lane (the butterfly's
-/// stride-1 step), strides 2, 4, ... follow over the kLw lanes of the row — the same sum, bit for
-/// bit. Half the lanes per row means half the addressing and butterfly work per row; measured, a
-/// wave gains 1.5-4 % from it and the first round loses 1-3 %, so only the waves use it.
+/// Eight int8 codes (two 32-bit words) against eight (scale, query) pairs: sum of
+/// (code * scale - q)^2 with two fused multiply-adds per code, in code order. The int8 -> float
+/// conversion: one byte permute makes the fp16 patterns 0x64bb = 1024 + (code + 128) of two codes,
+/// and the mixed-precision subtract of 1152 gives each code exactly, off the conversion pipe.
+__device__ __forceinline__ float sketch_chunk8(unsigned w0, unsigned w1, const float* s, const float* q)
+{
+  const unsigned x0 = w0 ^ 0x80808080u, x1 = w1 ^ 0x80808080u;  // code + 128 in every byte
+  float d           = 0.f;
+#pragma unroll
+  for (int p = 0; p < 4; p++) {
+    const unsigned hh = __byte_perm(p < 2 ? x0 : x1, 0x64646464u, (p & 1) ? 0x4342 : 0x4140);
+    const float c0    = half_minus(static_cast<unsigned short>(hh & 0xffffu), 1152.0f);
+    const float c1    = half_minus(static_cast<unsigned short>(hh >> 16), 1152.0f);
+    const float t0    = __fmaf_rn(c0, s[2 * p], -q[2 * p]);
+    d                 = __fmaf_rn(t0, t0, d);
+    const float t1    = __fmaf_rn(c1, s[2 * p + 1], -q[2 * p + 1]);
+    d                 = __fmaf_rn(t1, t1, d);
+  }
+  return d;
+}
+
+/// The sketch distance in the reference's own fp32 terms, sum_k (c_k s_k - q_k)^2
+/// (search_kernels.cuh:228-251), for the waves: there a candidate's row arrives from memory later
+/// than the arithmetic on it takes, so the form that needs nothing but the row (no row constant)
+/// is the faster one; the first round, whose rows are mostly in the L2 cache already, is bound by
+/// instructions and takes the integer form above. Summation order (shared with the CPU checker):
+/// chunk c of 8 codes is partial sum c (two fused multiply-adds per code, in code order), a
+/// butterfly over the next power of two >= S / 8 partial sums with strides 1, 2, 4, ... A lane
+/// holds two neighbouring chunks (one 16-byte load) and adds them itself (stride 1); kLw (a power
+/// of two >= S / 16) lanes own a row; two rows per lane group are in flight. A lane past the last
+/// chunk works on chunk 0 with scales and query 0 and adds exactly 0.
 template <int kLw, bool kDealt>
-__device__ __forceinline__ void sketch_rows16(const int* cand, int n, const signed char* __restrict__ sketch,
-                                              const row_map& map, const float* sc, const float* qv,
-                                              float* dist)
+__device__ __forceinline__ void sketch_rows_f32(const int* cand, int n, const signed char* __restrict__ sketch,
+                                                const row_map& map, int S, const float* sc, const float* qv,
+                                                float* dist)
 {
   constexpr int kG = 32 / kLw;  // rows per warp and step
-  constexpr int S  = 16 * kLw;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   const int sub = lane % kLw, grp = lane / kLw;
+  const bool live = 16 * sub < S;
+  const int subc  = live ? sub : 0;
   float cs[16], cq[16];
 #pragma unroll
   for (int b = 0; b < 16; b++) {
-    cs[b] = sc[sub * 16 + b];
-    cq[b] = qv[sub * 16 + b];
+    cs[b] = live ? sc[sub * 16 + b] : 0.f;
+    cq[b] = live ? qv[sub * 16 + b] : 0.f;
   }
   const int rpp = nw * kG;  // rows per step of the block
   for (int jb = 0; jb < n; jb += 2 * rpp) {
@@ -372,12 +571,12 @@ __device__ __forceinline__ void sketch_rows16(const int* cand, int n, const sign
     for (int u = 0; u < 2; u++) {
       j[u]         = jb + u * rpp + warp * kG + grp;
       const int id = cand[min(j[u], n - 1)];
-      w[u] = __ldg(reinterpret_cast<const uint4*>(row_of<kDealt>(sketch, map, id, S)) + sub);
+      w[u] = __ldg(reinterpret_cast<const uint4*>(row_of<kDealt>(sketch, map, id, S)) + subc);
     }
 #pragma unroll
     for (int u = 0; u < 2; u++) {
-      const float d0 = sketch_chunk8(make_uint2(w[u].x, w[u].y), cs, cq);
-      const float d1 = sketch_chunk8(make_uint2(w[u].z, w[u].w), cs + 8, cq + 8);
+      const float d0 = sketch_chunk8(w[u].x, w[u].y, cs, cq);
+      const float d1 = sketch_chunk8(w[u].z, w[u].w, cs + 8, cq + 8);
       float d        = __fadd_rn(d0, d1);
 #pragma unroll
       for (int o = 1; o < kLw; o <<= 1)
@@ -558,35 +757,45 @@ __device__ __forceinline__ void merge_into_kept(unsigned long long* pool,
   __syncthreads();
   const int total = nk + ctrl[6];
   int cnt         = min(total, KO);
-  int width       = P;  // keys handed to the sort
+  constexpr int kRankMax = 128;  // keys sorted by ranking, one thread per key (blocks have >= 128 threads)
   if (total <= 2 * P) {
-    while (width < total)
-      width <<= 1;
-    for (int i = threadIdx.x; i < max(width, 64); i += blockDim.x)
-      sorted[i] = i < total ? pool[i] : kNoKey;
+    if (total <= kRankMax) {
+      rank_sort(pool, total, sorted);
+    } else {
+      int width = P;
+      while (width < total)
+        width <<= 1;
+      for (int i = threadIdx.x; i < width; i += blockDim.x)
+        sorted[i] = i < total ? pool[i] : kNoKey;
+      __syncthreads();
+      bitonic_sort(sorted, width);
+    }
   } else {
+    // the KO smallest are cut out first (into the upper half of the sort region), then sorted
+    unsigned long long* picked = sorted + max(P, 32);
     auto hi_at          = [&](int i) { return static_cast<unsigned>(pool[i] >> 32); };
     auto lo_at          = [&](int i) { return static_cast<unsigned>(pool[i]); };
-    const radix_cut_t c = radix_cut(hi_at, lo_at, total, KO, hist, ctrl);
+    const radix_cut_t c = smallest_cut(hi_at, lo_at, total, KO, hist, ctrl);
     if (threadIdx.x == 0) ctrl[0] = 0;
     __syncthreads();
     for (int i = threadIdx.x; i < total; i += blockDim.x) {
       const unsigned long long k = pool[i];
       if ((k & c.mask) <= c.prefix) {
         const int s = atomicAdd(&ctrl[0], 1);
-        if (s < P) sorted[s] = k;
+        if (s < P) picked[s] = k;
       }
     }
-    for (int i = KO + threadIdx.x; i < max(P, 64); i += blockDim.x)
-      sorted[i] = kNoKey;
+    __syncthreads();
+    if (KO <= kRankMax) {
+      rank_sort(picked, KO, sorted);
+    } else {
+      for (int i = threadIdx.x; i < P; i += blockDim.x)
+        sorted[i] = i < KO ? picked[i] : kNoKey;
+      __syncthreads();
+      bitonic_sort(sorted, P);
+    }
   }
   __syncthreads();
-  if (width <= 64) {  // short lists: one warp sorts 64 keys in registers, no barrier per step
-    if (threadIdx.x < 32) warp_sort64(sorted);
-    __syncthreads();
-  } else {
-    bitonic_sort(sorted, width);
-  }
   for (int i = threadIdx.x; i < KO; i += blockDim.x) {
     const unsigned long long k = i < cnt ? sorted[i] : kNoKey;
     pb[i] = k == kNoKey ? -1 : static_cast<long long>(static_cast<unsigned>(k & 0xffffffffULL));
@@ -612,23 +821,32 @@ __global__ void __launch_bounds__(kThreads, 1024 / kThreads) round_kernel(const 
   unsigned long long* sorted = reinterpret_cast<unsigned long long*>(smem + lay.sorted);
   int* sid                   = smem + lay.sid;
   float* sdv                 = reinterpret_cast<float*>(smem + lay.sdv);
-  float* qv                  = reinterpret_cast<float*>(smem + lay.qv);
-  float* sc                  = reinterpret_cast<float*>(smem + lay.sc);
+  int* w16                   = smem + lay.qv;
+  float* kq                  = reinterpret_cast<float*>(smem + lay.sc);
   float* fq                  = reinterpret_cast<float*>(smem + lay.fq);
   int* st                    = smem + lay.st;
   int* len                   = smem + lay.len;
   unsigned* hist             = reinterpret_cast<unsigned*>(smem + lay.hist);
   int* wsum                  = smem + lay.wsum;
   int* ctrl                  = smem + lay.ctrl;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int S    = a.sw;
   long long* pb  = a.si + static_cast<int64_t>(q) * a.KO;
   float* pd      = a.sd + static_cast<int64_t>(q) * a.KO;
   const bool fresh = a.fresh != 0;
 
-  for (int i = threadIdx.x; i < S; i += blockDim.x) {
-    qv[i] = a.qs[static_cast<int64_t>(q) * S + i];
-    sc[i] = a.scale[i];
+  // The integer form of the sketch distance serves the first round of a search that reranks
+  // exactly. Waves take the fp32 sum (see sketch_rows_f32), and so does every round of a search
+  // that ranks by sketch distance: there the distances of all rounds meet in one kept list, where
+  // an id found twice must bring the same key both times.
+  const bool int_form = !kRows && !a.sketch_rank;
+  if (int_form) {
+    if (warp == 0) sketch_query_setup(a.qs + static_cast<int64_t>(q) * S, a.scale, S, w16, kq);
+  } else {
+    for (int i = threadIdx.x; i < S; i += blockDim.x) {
+      reinterpret_cast<float*>(w16)[i] = a.qs[static_cast<int64_t>(q) * S + i];
+      kq[i]                            = a.scale[i];
+    }
   }
   if (!a.sketch_rank)
     for (int i = threadIdx.x; i < a.D; i += blockDim.x)
@@ -754,6 +972,9 @@ __global__ void __launch_bounds__(kThreads, 1024 / kThreads) round_kernel(const 
     const int within0 = threadIdx.x & (lps - 1);
     const int spp     = kThreads / lps;  // segments per pass
     const int seg0    = threadIdx.x / lps;
+    // the large arrays pass through the L2 cache without staying when the sketch is to be kept there
+    const bool stream = a.keep_sketch != 0 && (!kDealt || !kRows || a.table_map.ptrs == nullptr);
+    const unsigned long long spol = l2_policy_stream();
     // loop bounds are the same for every thread: the slot counter below is updated once per warp
     for (int wb = 0; wb < maxlen; wb += lps) {
       const int w0 = wb + within0;
@@ -765,9 +986,11 @@ __global__ void __launch_bounds__(kThreads, 1024 / kThreads) round_kernel(const 
           v[u]        = -1;
           if (s < nseg && w0 < maxlen) {
             if constexpr (kRows) {
-              v[u] = __ldg(row_of<kDealt>(a.table, a.table_map, st[s], a.table_len) + w0);
+              const int* at = row_of<kDealt>(a.table, a.table_map, st[s], a.table_len) + w0;
+              v[u]          = stream ? ldg_i32_hint(at, spol) : __ldg(at);
             } else {
-              if (w0 < len[s]) v[u] = __ldg(a.lists + static_cast<int64_t>(s) * a.stride + st[s] + w0);
+              const int* at = a.lists + static_cast<int64_t>(s) * a.stride + st[s] + w0;
+              if (w0 < len[s]) v[u] = stream ? ldg_i32_hint(at, spol) : __ldg(at);
             }
           }
         }
@@ -783,8 +1006,12 @@ __global__ void __launch_bounds__(kThreads, 1024 / kThreads) round_kernel(const 
               if (prev == -1) {
                 is_new = true;
                 // the sketch row of a new id will be wanted soon: start bringing it into L2
-                if (may_prefetch<kDealt>(a.sketch_map))
-                  asm volatile("prefetch.global.L2 [%0];" ::"l"(a.sketch + static_cast<int64_t>(id) * S));
+                if (may_prefetch<kDealt>(a.sketch_map)) {
+                  if (a.keep_sketch)
+                    asm volatile("prefetch.global.L2::evict_last [%0];" ::"l"(a.sketch + static_cast<int64_t>(id) * S));
+                  else
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(a.sketch + static_cast<int64_t>(id) * S));
+                }
                 break;
               }
               if (prev == id) break;
@@ -819,73 +1046,37 @@ __global__ void __launch_bounds__(kThreads, 1024 / kThreads) round_kernel(const 
   const int n = min(ctrl[4], a.nmax);
   tick(1);
 
-  // int8 sketch distances (search_kernels.cuh:228-251): one 8-code chunk per lane with its scale and
-  // query coordinates in registers, the chunks of a row summed by a butterfly over its lanes
-  // (strides 1, 2, 4, ...); four rows per lane group in flight. A sketch wider than 256 gives a
-  // lane a second chunk (c + 32), added last.
-  if (kRows && S == 64) {
-    sketch_rows16<4, kDealt>(cand, n, a.sketch, a.sketch_map, sc, qv, dist);
-  } else if (kRows && S == 128) {
-    sketch_rows16<8, kDealt>(cand, n, a.sketch, a.sketch_map, sc, qv, dist);
-  } else if (S == 64) {
-    sketch_rows<8, kDealt, true>(cand, n, a.sketch, a.sketch_map, S, sc, qv, dist);
-  } else if (S == 128) {
-    sketch_rows<16, kDealt, true>(cand, n, a.sketch, a.sketch_map, S, sc, qv, dist);
-  } else if (S <= 8) {
-    sketch_rows<1, kDealt>(cand, n, a.sketch, a.sketch_map, S, sc, qv, dist);
-  } else if (S <= 16) {
-    sketch_rows<2, kDealt>(cand, n, a.sketch, a.sketch_map, S, sc, qv, dist);
-  } else if (S <= 32) {
-    sketch_rows<4, kDealt>(cand, n, a.sketch, a.sketch_map, S, sc, qv, dist);
-  } else if (S <= 64) {
-    sketch_rows<8, kDealt>(cand, n, a.sketch, a.sketch_map, S, sc, qv, dist);
-  } else if (S <= 128) {
-    sketch_rows<16, kDealt>(cand, n, a.sketch, a.sketch_map, S, sc, qv, dist);
-  } else if (S <= 256) {
-    sketch_rows<32, kDealt>(cand, n, a.sketch, a.sketch_map, S, sc, qv, dist);
-  } else {
-    // wider than 256: a lane takes a second chunk (c + 32), added last
-    const int chunks = S / 8;
-    int Lw           = 1;
-    while (Lw < chunks && Lw < 32)
-      Lw <<= 1;
-    const int G = 32 / Lw, sub = lane % Lw;
-    const int rpp    = nw * G;  // rows per pass of the block
-    const bool live  = sub < chunks;
-    const bool live2 = sub + 32 < chunks;
-    float cs[8], cq[8];
-#pragma unroll
-    for (int b = 0; b < 8; b++) {
-      cs[b] = live ? sc[sub * 8 + b] : 0.f;
-      cq[b] = live ? qv[sub * 8 + b] : 0.f;
+  // int8 sketch distances (search_kernels.cuh:228-251), sixteen codes per lane, S / 16 lanes
+  // (rounded up to a power of two) per row
+  if (!int_form) {
+    const float* qv = reinterpret_cast<const float*>(w16);
+    if (S <= 16) {
+      sketch_rows_f32<1, kDealt>(cand, n, a.sketch, a.sketch_map, S, kq, qv, dist);
+    } else if (S <= 32) {
+      sketch_rows_f32<2, kDealt>(cand, n, a.sketch, a.sketch_map, S, kq, qv, dist);
+    } else if (S <= 64) {
+      sketch_rows_f32<4, kDealt>(cand, n, a.sketch, a.sketch_map, S, kq, qv, dist);
+    } else if (S <= 128) {
+      sketch_rows_f32<8, kDealt>(cand, n, a.sketch, a.sketch_map, S, kq, qv, dist);
+    } else if (S <= 256) {
+      sketch_rows_f32<16, kDealt>(cand, n, a.sketch, a.sketch_map, S, kq, qv, dist);
+    } else {
+      sketch_rows_f32<32, kDealt>(cand, n, a.sketch, a.sketch_map, S, kq, qv, dist);
     }
-    for (int jb = 0; jb < n; jb += 4 * rpp) {
-      uint2 w[4];
-      int j[4];
-#pragma unroll
-      for (int u = 0; u < 4; u++) {
-        j[u] = jb + u * rpp + warp * G + lane / Lw;
-        if (j[u] < n && live)
-          w[u] = __ldg(reinterpret_cast<const uint2*>(row_of<kDealt>(a.sketch, a.sketch_map, cand[j[u]], S) + sub * 8));
-      }
-#pragma unroll
-      for (int u = 0; u < 4; u++) {
-        float d = (j[u] < n && live) ? sketch_chunk8(w[u], cs, cq) : 0.f;
-        for (int o = 1; o < Lw; o <<= 1)
-          d = __fadd_rn(d, __shfl_xor_sync(0xffffffffu, d, o));
-        if (chunks > 32) {
-          float e = 0.f;
-          if (j[u] < n && live2) {
-            const uint2 w2 = __ldg(reinterpret_cast<const uint2*>(
-              row_of<kDealt>(a.sketch, a.sketch_map, cand[j[u]], S) + (sub + 32) * 8));
-            e = sketch_chunk8(w2, sc + (sub + 32) * 8, qv + (sub + 32) * 8);
-          }
-          for (int o = 1; o < 32; o <<= 1)
-            e = __fadd_rn(e, __shfl_xor_sync(0xffffffffu, e, o));
-          d = __fadd_rn(d, e);
-        }
-        if (j[u] < n && sub == 0) dist[j[u]] = d;
-      }
+  } else {
+    const bool keep = a.keep_sketch != 0 && may_prefetch<kDealt>(a.sketch_map);
+    if (S <= 16) {
+      sketch_rows_int<1, kDealt>(cand, n, a.sketch, a.sketch_norm, a.sketch_map, S, w16, kq, dist, keep);
+    } else if (S <= 32) {
+      sketch_rows_int<2, kDealt>(cand, n, a.sketch, a.sketch_norm, a.sketch_map, S, w16, kq, dist, keep);
+    } else if (S <= 64) {
+      sketch_rows_int<4, kDealt>(cand, n, a.sketch, a.sketch_norm, a.sketch_map, S, w16, kq, dist, keep);
+    } else if (S <= 128) {
+      sketch_rows_int<8, kDealt>(cand, n, a.sketch, a.sketch_norm, a.sketch_map, S, w16, kq, dist, keep);
+    } else if (S <= 256) {
+      sketch_rows_int<16, kDealt>(cand, n, a.sketch, a.sketch_norm, a.sketch_map, S, w16, kq, dist, keep);
+    } else {
+      sketch_rows_int<32, kDealt>(cand, n, a.sketch, a.sketch_norm, a.sketch_map, S, w16, kq, dist, keep);
     }
   }
   __syncthreads();
@@ -906,7 +1097,7 @@ __global__ void __launch_bounds__(kThreads, 1024 / kThreads) round_kernel(const 
     auto key_at = [&](int i) { return rank_key(dist[i], static_cast<unsigned>(cand[i])); };
     auto hi_at          = [&](int i) { return __float_as_uint(dist[i]); };
     auto lo_at          = [&](int i) { return static_cast<unsigned>(cand[i]); };
-    const radix_cut_t c = radix_cut(hi_at, lo_at, n, R, hist, ctrl);
+    const radix_cut_t c = smallest_cut(hi_at, lo_at, n, R, hist, ctrl);
     if (threadIdx.x == 0) ctrl[0] = 0;
     __syncthreads();
     for (int i = threadIdx.x; i < n; i += blockDim.x) {

@@ -46,7 +46,8 @@ constexpr size_t kSmemSoftLimit = size_t{96} << 10;   // above this the candidat
 constexpr size_t kSmemHardLimit = size_t{227} << 10;  // shared memory a block can opt in to
 
 /// Fill the size fields of a round and decide where its candidate arrays live.
-void size_round(plan& pl, kernels::round_args& r, int entries_max, int pick_entries, int device)
+void size_round(plan& pl, kernels::round_args& r, int entries_max, int pick_entries, int device,
+                int64_t sketch_bytes)
 {
   r.pick_slots = 0;
   if (pick_entries > 0) {
@@ -94,6 +95,12 @@ void size_round(plan& pl, kernels::round_args& r, int entries_max, int pick_entr
   const size_t per_block = kernels::round_smem_bytes(r) + 1024;
   const int fit          = static_cast<int>(std::max<size_t>((size_t{228} << 10) / per_block, 1));
   r.threads              = fit >= 8 ? 128 : fit >= 4 ? 256 : 512;
+  {
+    // the sketch stays in the L2 cache when it and its constants take at most 60 % of it
+    int l2 = 0;
+    OCTEX_CUDA_TRY(cudaDeviceGetAttribute(&l2, cudaDevAttrL2CacheSize, device));
+    r.keep_sketch = sketch_bytes > 0 && static_cast<double>(sketch_bytes) <= 0.6 * l2 ? 1 : 0;
+  }
 }
 
 }  // namespace
@@ -118,8 +125,9 @@ void check_tc(plan const& pl)
   if (pl.tc_error_host == nullptr || *pl.tc_error_host == 0) return;
   const int code    = *pl.tc_error_host;
   *pl.tc_error_host = 0;
-  throw error("octex: the projection kernel gave up waiting for its operands (code " +
-              std::to_string(code) + "); the results of that batch are not valid");
+  throw error("octex: a kernel gave up waiting for data it had asked for (code " + std::to_string(code) +
+              ": 1, 2 the projection's operands, 3 the segments of a gather, 4 the rows of a rerank); "
+              "the results of that batch are not valid");
 }
 
 /// Launch every kernel of a batch on s (captured into the graph, or run directly).
@@ -212,8 +220,10 @@ void run_batch(index_impl const& ix, plan& pl, cudaStream_t s, std::vector<cudaE
       c.recv(rd, pl.mw * e * sizeof(float), r, s);
     }
     c.group_end();
+    mark();
     kernels::merge_kept(pl.recv_i.as<long long>(), pl.recv_d.as<float>(), pl.world,
                         int64_t{pl.mwmax} * pl.KO, pl.KO, pl.P_merge, pl.mw, pl.wsi, pl.wsd, s);
+    mark();
   }
   if (pl.dbg.taps && pl.mw > 0) {
     OCTEX_CUDA_TRY(cudaMemcpyAsync(pl.kept1_i.ptr, pl.wsi, sizeof(long long) * pl.mw * pl.KO,
@@ -230,16 +240,16 @@ void run_batch(index_impl const& ix, plan& pl, cudaStream_t s, std::vector<cudaE
   }
   if (pl.sp.sketch_rank && pl.FR > 0) {
     kernels::final_rerank(pl.wsi, pl.KO, pl.FR, p.vectors.as<__half>(), pl.r1.vector_map, D, Qw, pl.k,
-                          pl.mw, pl.bi.as<long long>(), pl.bd.as<float>(), pl.stats.as<long long>(), s);
+                          pl.mw, pl.bi, pl.bd, pl.stats.as<long long>(), s);
   } else {
-    kernels::take_k(pl.wsi, pl.wsd, pl.KO, pl.k, pl.mw, pl.bi.as<long long>(), pl.bd.as<float>(), s);
+    kernels::take_k(pl.wsi, pl.wsd, pl.KO, pl.k, pl.mw, pl.bi, pl.bd, s);
   }
   mark();
   if (pl.world > 1) {
     // every process gets the results of all slices (blocks of mwmax rows, the last rows of a
     // block unused when the slices differ in size)
-    ix.comm->all_gather(pl.bi.ptr, pl.gi.ptr, sizeof(long long) * pl.mwmax * pl.k, s);
-    ix.comm->all_gather(pl.bd.ptr, pl.gd.ptr, sizeof(float) * pl.mwmax * pl.k, s);
+    ix.comm->all_gather(pl.out.ptr, pl.gathered.ptr, pl.out_block, s);
+    mark();
   }
   OCTEX_CUDA_TRY(cudaPeekAtLastError());
 }
@@ -342,10 +352,11 @@ auto make_plan(index_impl& ix, search_params const& sp, int m, int k, debug_opti
   pl.qs    = alloc<float>(pl, p.device, int64_t{m1} * sw);
   pl.use_tc = !dbg.ordered_projection && kernels::project_tc_supported(ix.blocks, p.ldu);
   if (!pl.use_tc || dbg.taps) pl.Y = alloc<__half>(pl, p.device, int64_t{m1} * wdt);
+  // the word a kernel sets when one of its bounded waits (on an mbarrier) ran out
+  OCTEX_CUDA_TRY(cudaHostAlloc(reinterpret_cast<void**>(&pl.tc_error_host), sizeof(int), cudaHostAllocMapped));
+  *pl.tc_error_host = 0;
+  OCTEX_CUDA_TRY(cudaHostGetDevicePointer(reinterpret_cast<void**>(&pl.tc_error_dev), pl.tc_error_host, 0));
   if (pl.use_tc) {
-    OCTEX_CUDA_TRY(cudaHostAlloc(reinterpret_cast<void**>(&pl.tc_error_host), sizeof(int), cudaHostAllocMapped));
-    *pl.tc_error_host = 0;
-    OCTEX_CUDA_TRY(cudaHostGetDevicePointer(reinterpret_cast<void**>(&pl.tc_error_dev), pl.tc_error_host, 0));
     kernels::project_tc_setup(pl.tc, pl.qh.as<__half>(), m1, p.ut.as<__half>(), p.copies, p.ldu);
   }
   pl.codes = alloc<long long>(pl, p.device, int64_t{m1} * p.copies * L);
@@ -353,8 +364,13 @@ auto make_plan(index_impl& ix, search_params const& sp, int m, int k, debug_opti
   pl.si    = alloc<long long>(pl, p.device, int64_t{m1} * pl.KO, 0xff);
   pl.sd    = alloc<float>(pl, p.device, int64_t{m1} * pl.KO);
   const int mwmax = std::max(pl.mwmax, 1);
-  pl.bi    = alloc<long long>(pl, p.device, int64_t{mwmax} * k, 0xff);
-  pl.bd    = alloc<float>(pl, p.device, int64_t{mwmax} * k, 0);
+  // the results of this process's slice: ids [mwmax, k], then distances [mwmax, k], in one block so
+  // that one collective moves both
+  pl.out_ids = sizeof(long long) * static_cast<size_t>(mwmax) * k;
+  pl.out_block = pl.out_ids + sizeof(float) * static_cast<size_t>(mwmax) * k;
+  pl.out   = alloc<char>(pl, p.device, static_cast<int64_t>(pl.out_block), 0xff);
+  pl.bi    = pl.out.as<long long>();
+  pl.bd    = reinterpret_cast<float*>(pl.out.as<char>() + pl.out_ids);
   pl.wsi   = pl.si.as<long long>();
   pl.wsd   = pl.sd.as<float>();
   if (pl.shard) {
@@ -369,8 +385,7 @@ auto make_plan(index_impl& ix, search_params const& sp, int m, int k, debug_opti
       pl.P_merge <<= 1;
   }
   if (ix.world > 1) {
-    pl.gi = alloc<long long>(pl, p.device, int64_t{ix.world} * mwmax * k, 0xff);
-    pl.gd = alloc<float>(pl, p.device, int64_t{ix.world} * mwmax * k, 0);
+    pl.gathered = alloc<char>(pl, p.device, static_cast<int64_t>(pl.out_block) * ix.world, 0xff);
   }
   if (sp.waves > 0) pl.done = alloc<int>(pl, p.device, int64_t{m1} * S * sp.waves, 0xff);
   if (dbg.stats) {
@@ -396,6 +411,7 @@ auto make_plan(index_impl& ix, search_params const& sp, int m, int k, debug_opti
   r1.stride      = p.stride;
   r1.lr          = pl.lr;
   r1.sketch      = p.sketch.as<signed char>();
+  r1.sketch_norm = p.sketch_norm.as<float>();
   r1.scale       = p.scale.as<float>();
   r1.qs          = pl.qs.as<float>();
   r1.sw          = sw;
@@ -418,7 +434,9 @@ auto make_plan(index_impl& ix, search_params const& sp, int m, int k, debug_opti
     r1.tap_n    = pl.tap_n.as<int>();
     r1.tap_cap  = pl.tap_cap;
   }
-  size_round(pl, r1, p.copies * pl.lr, 0, p.device);
+  // sketch rows of this GPU's own memory (not the host tier, not dealt over GPUs) plus their constants
+  const int64_t sketch_bytes = (p.sketch.host || p.sketch_rows.on) ? 0 : static_cast<int64_t>(p.sketch.size + p.sketch_norm.size);
+  size_round(pl, r1, p.copies * pl.lr, 0, p.device, sketch_bytes);
   // waves: table rows of the start points
   if (sp.waves > 0) {
     auto& r2       = pl.r2;
@@ -433,6 +451,7 @@ auto make_plan(index_impl& ix, search_params const& sp, int m, int k, debug_opti
     r2.done        = pl.done.as<int>();
     r2.done_stride = S * sp.waves;
     r2.sketch      = r1.sketch;
+    r2.sketch_norm = r1.sketch_norm;
     r2.scale       = r1.scale;
     r2.qs          = r1.qs + static_cast<size_t>(pl.lo - pl.q1) * sw;
     r2.sw          = sw;
@@ -447,7 +466,7 @@ auto make_plan(index_impl& ix, search_params const& sp, int m, int k, debug_opti
     r2.sd          = pl.wsd;
     r2.stats       = r1.stats;
     r2.phase       = pl.phase2.as<long long>();
-    size_round(pl, r2, S * ix.table_len, S * std::max(sp.waves - 1, 0), p.device);
+    size_round(pl, r2, S * ix.table_len, S * std::max(sp.waves - 1, 0), p.device, sketch_bytes);
   }
   kernels::round_allow_smem(pl.smem_max);
 
@@ -557,9 +576,9 @@ void search_impl(resources const& res,
     else
       run_batch(ix, *pl, s, nullptr);  // use_graph = false, or a batch with exchanges
     if (!resident && pl->world == 1) {
-      OCTEX_CUDA_TRY(cudaMemcpyAsync(neighbors + b0 * k, pl->bi.ptr, sizeof(int64_t) * n * k,
+      OCTEX_CUDA_TRY(cudaMemcpyAsync(neighbors + b0 * k, pl->bi, sizeof(int64_t) * n * k,
                                      cudaMemcpyDefault, s));
-      OCTEX_CUDA_TRY(cudaMemcpyAsync(distances + b0 * k, pl->bd.ptr, sizeof(float) * n * k,
+      OCTEX_CUDA_TRY(cudaMemcpyAsync(distances + b0 * k, pl->bd, sizeof(float) * n * k,
                                      cudaMemcpyDefault, s));
     } else if (!resident) {
       // the gathered results: block r holds the rows [lo_r, hi_r) of the batch
@@ -568,10 +587,10 @@ void search_impl(resources const& res,
         const int hi_r = static_cast<int>(int64_t{m} * (r + 1) / pl->world);
         const int rows = std::clamp(n - lo_r, 0, hi_r - lo_r);
         if (rows == 0) continue;
-        const size_t at = static_cast<size_t>(r) * pl->mwmax * k;
-        OCTEX_CUDA_TRY(cudaMemcpyAsync(neighbors + (b0 + lo_r) * k, pl->gi.as<long long>() + at,
-                                       sizeof(int64_t) * rows * k, cudaMemcpyDefault, s));
-        OCTEX_CUDA_TRY(cudaMemcpyAsync(distances + (b0 + lo_r) * k, pl->gd.as<float>() + at,
+        const char* block = pl->gathered.as<char>() + static_cast<size_t>(r) * pl->out_block;
+        OCTEX_CUDA_TRY(cudaMemcpyAsync(neighbors + (b0 + lo_r) * k, block, sizeof(int64_t) * rows * k,
+                                       cudaMemcpyDefault, s));
+        OCTEX_CUDA_TRY(cudaMemcpyAsync(distances + (b0 + lo_r) * k, block + pl->out_ids,
                                        sizeof(float) * rows * k, cudaMemcpyDefault, s));
       }
     }

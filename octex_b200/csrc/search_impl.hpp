@@ -24,15 +24,19 @@ struct plan {
   int m1 = 0, q1 = 0, lo = 0, hi = 0, mw = 0, mwmax = 0;
   dbuf si2, sd2;        // shard: kept list of the own slice after the cross-process merge
   dbuf recv_i, recv_d;  // shard: [world, mwmax, KO] first-round kept lists of every process
-  dbuf gi, gd;          // world > 1: [world, mwmax, k] results of every process
+  dbuf out;             // results of this process's slice: ids [mwmax, k], then distances [mwmax, k]
+  dbuf gathered;        // world > 1: the out blocks of every process
+  size_t out_block = 0, out_ids = 0;  // bytes of a block and of its ids
+  long long* bi = nullptr;            // the two arrays inside out
+  float* bd     = nullptr;
   long long* wsi = nullptr;  // kept list the waves work on [mw, KO]
   float* wsd     = nullptr;
   int P_merge    = 0;   // keys sorted by the cross-process merge (power of two >= world * KO)
-  dbuf qbuf, qh, qs, Y, codes, seg, si, sd, done, bi, bd, stats, phase1, phase2;
+  dbuf qbuf, qh, qs, Y, codes, seg, si, sd, done, stats, phase1, phase2;
   dbuf tap_cand, tap_dist, tap_n, kept1_i, kept1_d;
   bool use_tc = false;          // tensor-core projection with the decode in its epilogue
   kernels::project_tc_plan tc;  // its tensor maps
-  int* tc_error_host = nullptr; // pinned, device-visible: non-zero when a wait in that kernel ran out
+  int* tc_error_host = nullptr; // pinned, device-visible: non-zero when a bounded wait in a kernel ran out
   int* tc_error_dev  = nullptr;
   int tap_cap = 0;
   std::vector<dbuf> scratch_cand, scratch_dist;

@@ -364,8 +364,14 @@ class Index:
         _lib.check(_lib.lib().octexB200ProfileBatch(C.c_size_t(0), C.byref(p), self._h,
                                                     C.c_int64(n_queries), C.c_int64(k), ms,
                                                     C.c_int32(64), C.byref(n)))
+        waves = int(p.waves)
         names = ["center_sketch", "project", "cell_codes", "probe", "round_lists"]
-        names += [f"round_rows[{i}]" for i in range(n.value - 6)] + ["best_k"]
+        extra = n.value - 6 - waves  # several processes: the exchanges are timed on their own
+        if extra >= 3:
+            names += ["exchange", "merge"]
+        names += [f"round_rows[{i}]" for i in range(waves)] + ["best_k"]
+        if extra in (1, 3):
+            names += ["gather_results"]
         return list(zip(names, [float(ms[i]) for i in range(n.value)]))
 
 

@@ -179,6 +179,73 @@ float sketch_distance(const int8_t* code, const float* scale, const float* qs, i
   return part[0];
 }
 
+// The same distance in the form the CUDA path evaluates it in the first round (where the candidates'
+// rows are mostly cached and the arithmetic is what costs; in the waves it evaluates the sum above),
+//   sum_k (c_k s_k - q_k)^2 = sum_k (c_k s_k)^2 - 2 sum_k c_k (s_k q_k) + sum_k q_k^2,
+// with the middle sum in integers: per query the products t_k = s_k q_k are scaled to 16-bit
+// weights w_k = rint(t_k / alpha), alpha = max |t_k| / 32000, so that sum_k c_k w_k is an exact
+// int32 dot product of int8 codes with int16 weights; the first sum is a per-row constant and the
+// last a per-query constant. Against the fp32 sum above the value differs by the rounding of the
+// weights (relative 1.6e-5 of the largest product per term) and of three fp32 operations; every
+// operation and its order are stated here and are the CUDA path's, so the two agree bit for bit.
+struct sketch_query {
+  std::vector<int32_t> w;  // [S] weights in [-32000, 32000]
+  float beta = 0.f;        // -2 alpha
+  float qq   = 0.f;        // sum of q_k^2: partial sum k mod 32, butterfly with strides 1 .. 16
+};
+
+sketch_query prepare_sketch_query(const float* scale, const float* qs, int S)
+{
+  sketch_query out;
+  out.w.resize(S);
+  std::vector<float> t(S);
+  float amax = 0.f;
+  for (int k = 0; k < S; k++) {
+    t[k] = scale[k] * qs[k];
+    amax = std::fmax(amax, std::fabs(t[k]));  // fmax ignores a NaN operand, as fmaxf on the GPU
+  }
+  const float alpha = (amax > 0.f && std::isfinite(amax)) ? amax / 32000.0f : 1.0f;
+  for (int k = 0; k < S; k++) {
+    const float r = std::nearbyint(t[k] / alpha);  // round to nearest even
+    out.w[k] = std::isnan(r) ? 0 : static_cast<int32_t>(std::fmin(std::fmax(r, -32000.0f), 32000.0f));
+  }
+  out.beta = -2.0f * alpha;
+  float part[32];
+  for (int p = 0; p < 32; p++)
+    part[p] = 0.f;
+  for (int k = 0; k < S; k++)
+    part[k & 31] = std::fma(qs[k], qs[k], part[k & 31]);
+  for (int o = 1; o < 32; o <<= 1) {
+    float nxt[32];
+    for (int p = 0; p < 32; p++)
+      nxt[p] = part[p] + part[p ^ o];
+    std::memcpy(part, nxt, sizeof(part));
+  }
+  out.qq = part[0];
+  return out;
+}
+
+// sum_k (c_k s_k)^2 of a row, one fused multiply-add per code in code order (a constant of the
+// row: the CUDA path computes it when the index is placed).
+float sketch_row_norm(const int8_t* code, const float* scale, int S)
+{
+  float n = 0.f;
+  for (int k = 0; k < S; k++) {
+    const float t = static_cast<float>(code[k]) * scale[k];
+    n = std::fma(t, t, n);
+  }
+  return n;
+}
+
+float sketch_distance_int(const int8_t* code, float norm, const sketch_query& sq, int S)
+{
+  int32_t dot = 0;
+  for (int k = 0; k < S; k++)
+    dot += static_cast<int32_t>(code[k]) * sq.w[k];
+  const float d = norm + std::fma(sq.beta, static_cast<float>(dot), sq.qq);
+  return std::fmax(d, 0.f);  // rounding may leave a tiny negative value; keys order by bit pattern
+}
+
 struct kept_list {
   std::vector<int64_t> id;
   std::vector<float> d;
@@ -367,13 +434,21 @@ int oracle_search(const oracle_index* ixp,
       }
       if (tp.seg) std::memcpy(tp.seg + qi * C * 2, seg.data(), sizeof(int32_t) * 2 * C);
 
-      auto score = [&](std::vector<int32_t>& ids, std::vector<float>& sd) {
+      // The CUDA path scores the first round's candidates in the integer form and the waves' in
+      // the fp32 sum when it reranks exactly; when it ranks by sketch distance (the distances of
+      // all rounds meet in one kept list, where an id found twice must bring the same key both
+      // times) every round takes the fp32 sum. sketch_form 1: the fp32 sum always, the reference's.
+      const sketch_query sq = prepare_sketch_query(ix.scale, sc.qs.data(), S);
+      auto score = [&](std::vector<int32_t>& ids, std::vector<float>& sd, bool first_round) {
         std::sort(ids.begin(), ids.end());
         ids.erase(std::unique(ids.begin(), ids.end()), ids.end());
         sd.resize(ids.size());
-        for (size_t i = 0; i < ids.size(); i++)
-          sd[i] = sketch_distance(ix.sketch + static_cast<int64_t>(ids[i]) * S, ix.scale,
-                                  sc.qs.data(), S);
+        for (size_t i = 0; i < ids.size(); i++) {
+          const int8_t* row = ix.sketch + static_cast<int64_t>(ids[i]) * S;
+          sd[i] = (sp.sketch_form == 1 || !first_round || sp.sketch_rank)
+                    ? sketch_distance(row, ix.scale, sc.qs.data(), S)
+                    : sketch_distance_int(row, sketch_row_norm(row, ix.scale, S), sq, S);
+        }
       };
       auto keep = [&](kept_list& kept, bool fresh, int R) {
         // exact mode: rerank_keep_kernel (search_kernels.cuh:421-467);
@@ -402,7 +477,7 @@ int oracle_search(const oracle_index* ixp,
             sc.ids.push_back(lp[i]);
           st_entries += seg[2 * c + 1];
         }
-        score(sc.ids, sc.sd);
+        score(sc.ids, sc.sd, true);
         st_n1 += static_cast<int64_t>(sc.ids.size());
         if (tp.cand1) {
           for (size_t i = 0; i < sc.ids.size() && cand_at < tp.cand_cap; i++, cand_at++) {
@@ -457,7 +532,7 @@ int oracle_search(const oracle_index* ixp,
             if (tr[i] >= 0) sc.ids.push_back(tr[i]);
         }
         st_rows += static_cast<int64_t>(starts.size());
-        score(sc.ids, sc.sd);
+        score(sc.ids, sc.sd, false);
         st_n2 += static_cast<int64_t>(sc.ids.size());
         keep(kept, false, sp.wave_rerank);
       }

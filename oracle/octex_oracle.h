@@ -35,6 +35,10 @@ typedef struct {
   int32_t sketch_rank, final_rerank;
   int32_t parts;   /* GPUs of a sharded placement emulated (1: no cross-part merge) */
   int32_t threads; /* host threads (0: all) */
+  int32_t sketch_form; /* 0: the sketch distance as the CUDA path computes it: the integer form
+                          (sketch_distance_int in octex_oracle.cpp) in the first round of a search
+                          that reranks exactly, the fp32 sum (code * scale - q)^2 otherwise;
+                          1: the fp32 sum in every round, the reference's own terms */
 } oracle_params;
 
 /* Optional observation points; any pointer may be NULL. */

@@ -32,7 +32,7 @@ class OracleParams(C.Structure):
     _fields_ = [("read", C.c_int32), ("starts", C.c_int32), ("waves", C.c_int32),
                 ("rerank", C.c_int32), ("wave_rerank", C.c_int32), ("batch", C.c_int32),
                 ("sketch_rank", C.c_int32), ("final_rerank", C.c_int32),
-                ("parts", C.c_int32), ("threads", C.c_int32)]
+                ("parts", C.c_int32), ("threads", C.c_int32), ("sketch_form", C.c_int32)]
 
 
 class OracleTaps(C.Structure):
@@ -160,15 +160,18 @@ class Index:
         self.struct = s
 
     def search(self, queries, k=10, read=32, starts=128, waves=2, rerank=128, wave_rerank=128,
-               sketch_rank=False, final_rerank=32, parts=1, threads=0, taps=(), y_in=None):
-        """Returns (neighbors, distances, taps dict)."""
+               sketch_rank=False, final_rerank=32, parts=1, threads=0, taps=(), y_in=None,
+               sketch_form="product"):
+        """Returns (neighbors, distances, taps dict).  ``sketch_form``: "product" evaluates the
+        sketch distance in the integer form of the CUDA path (bit-comparable with it),
+        "reference" as the fp32 sum of the reference's kernel."""
         q = np.ascontiguousarray(queries, np.float32)
         nq = q.shape[0]
         m = self.meta
         C_, w, L = m["copies"], 8 * m["blocks"], len(m["spacings"])
         KO = max(starts, k)
         sp = OracleParams(read, starts, waves, rerank, wave_rerank, 10000, int(sketch_rank),
-                          final_rerank, parts, threads)
+                          final_rerank, parts, threads, 1 if sketch_form == "reference" else 0)
         nb = np.zeros((nq, k), np.int64)
         ds = np.zeros((nq, k), np.float32)
         out = {}

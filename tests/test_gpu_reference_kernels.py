@@ -40,14 +40,17 @@ def test_checker_matches_reference_kernels(oracle, small_index, wide_index, whic
     full = dict(rerank=128, wave_rerank=128)
     full.update(kw)
     ref = oracle.ref_search_pipeline(arrays, meta, y, qs, queries, 10, **full)
+    # the checker evaluates the sketch distance in the reference's own fp32 terms here
     best_ids, best_dist, t = oracle.Index(arrays, meta).search(
-        queries, 10, y_in=y, taps=("seg", "cand1", "kept1_ids", "kept1_dist"), **kw)
+        queries, 10, y_in=y, taps=("seg", "cand1", "kept1_ids", "kept1_dist"),
+        sketch_form="reference", **kw)
     stages = [(ref["kept1_ids"], ref["kept1_dist"], t["kept1_ids"], t["kept1_dist"]),
               (ref["best_ids"], ref["best_dist"], best_ids, best_dist)]
     if not kw.get("sketch_rank"):
         # with k = KO the checker's result is its whole final kept list
         KO = max(kw["starts"], 10)
-        want_ids, want_dist, _ = oracle.Index(arrays, meta).search(queries, KO, y_in=y, **kw)
+        want_ids, want_dist, _ = oracle.Index(arrays, meta).search(queries, KO, y_in=y,
+                                                                   sketch_form="reference", **kw)
         stages.append((ref["kept_ids"], ref["kept_dist"], want_ids, want_dist))
 
     # cell lookup: identical segments

@@ -99,3 +99,30 @@ def test_errors(ox):
         ix.search(queries[:2], 10, read=0)
     with pytest.raises(RuntimeError, match="k >= 1"):
         ix.search(queries[:2], 0)
+
+
+def test_sketch_distance_forms_agree(oracle, small_index, wide_index):
+    """The sketch distance in the reference's fp32 terms, sum (c s - q)^2
+    (cpp/src/neighbors/octex/detail/search_kernels.cuh:228-251), and in the integer form the CUDA
+    path evaluates (row constant - 2 alpha * int8 x int16 dot product + query constant): values
+    within 1e-3 relative (the 16-bit weights; the sketch distance only ranks candidates for the
+    exact rerank), and the same neighbours from the same candidates."""
+    for arrays, meta, _, queries in (small_index, wide_index):
+        ix = oracle.Index(arrays, meta)
+        for kw in (dict(read=8, starts=32, waves=2, rerank=64, wave_rerank=64),
+                   dict(read=16, starts=16, waves=0, rerank=32)):
+            i0, d0, t0 = ix.search(queries, 10, taps=("cand1",), sketch_form="reference", **kw)
+            i1, d1, t1 = ix.search(queries, 10, taps=("cand1",), sketch_form="product", **kw)
+            assert np.array_equal(t0["cand1"], t1["cand1"])
+            held = t0["cand1"] >= 0
+            a, b = t0["cand1_dist"][held], t1["cand1_dist"][held]
+            assert (b >= 0).all()
+            assert np.max(np.abs(a - b) / (1.0 + np.abs(a))) < 1e-3
+            assert (i0 == i1).mean() >= 0.999
+            same = i0 == i1
+            assert np.allclose(d0[same], d1[same], rtol=1e-3)
+        # a search that ranks by sketch distance takes the fp32 sum in both forms: identical answers
+        kw = dict(read=8, starts=48, waves=1, sketch_rank=True, final_rerank=32)
+        i0, d0, _ = ix.search(queries, 10, sketch_form="reference", **kw)
+        i1, d1, _ = ix.search(queries, 10, sketch_form="product", **kw)
+        assert np.array_equal(i0, i1) and np.array_equal(d0, d1)

@@ -262,8 +262,18 @@ def run_reference(args, rank, world):
     import torch
     w = WORKLOADS[args.workload]
     base, queries = make_data(w, 0)
-    dev = "cuda" if torch.cuda.is_available() else "cpu"
-    arrays, meta = build_index.build_arrays(base, build_index.IndexParams(**w["build"]), device=dev)
+    if torch.cuda.is_available() and args.builder == "native":
+        # the same directory the other arm searches: the library's builder with the same seed
+        import shutil
+        import octex_b200
+        from octex_b200 import index_dir
+        path = os.path.join(args.index_dir, args.workload + "-reference-arm")
+        shutil.rmtree(path, ignore_errors=True)
+        octex_b200.build_native(base, path, **w["build"])
+        arrays, meta = index_dir.read_index(path)
+    else:
+        dev = "cuda" if torch.cuda.is_available() else "cpu"
+        arrays, meta = build_index.build_arrays(base, build_index.IndexParams(**w["build"]), device=dev)
     ox = oracle_py.Index(arrays, meta)
     sp = given_search(args) if args.search else dict(w.get("search", LADDER[args.ladder_start]))
     sample = queries[:args.cpu_sample]
@@ -401,6 +411,12 @@ def main():
     ap.add_argument("--workload", default="descriptor-1m", choices=sorted(WORKLOADS))
     ap.add_argument("--cpu-sample", type=int, default=2000)
     ap.add_argument("--ladder-start", type=int, default=0)
+    ap.add_argument("--builder", default="native", choices=["native", "torch"],
+                    help="native: the library's own GPU builder writes the index directory (to "
+                         "--index-dir) and the index is loaded from it; torch: the package's torch "
+                         "restatement of the builder makes the arrays in GPU memory")
+    ap.add_argument("--index-dir", default="/dev/shm/octex_b200_bench",
+                    help="where the native builder puts the index directory of the run")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-ref-kernels", action="store_true")
     ap.add_argument("--copies", type=int, default=0, help="override the copies of the build")
@@ -440,21 +456,48 @@ def main():
     base, queries = make_data(w, 0)  # every rank draws the same data: one index, one batch
     log(f"[rank {rank}] data {time.time() - t0:.1f}s")
     t0 = time.time()
-    arrays, meta = build_index.build_arrays(base, build_index.IndexParams(**w["build"]),
-                                            device=f"cuda:{local}", keep_on_device=True,
-                                            verbose=(rank == 0))
-    torch.cuda.synchronize()
-    log(f"[rank {rank}] index built in {time.time() - t0:.1f}s")
-    whole = octex_b200.attach(arrays, meta, borrow=True)  # the whole index on this GPU
-    if sharded:
-        from octex_b200 import dist as odist
-        rows = args.placement == "shard-rows"
-        idx = octex_b200.attach(arrays, meta, borrow=False, rank=rank, world=world, placement="shard",
-                                shard_vectors=rows, sketch="shard" if rows else "replicate")
-        odist.connect(idx)
+    build_seconds = None
+    if args.builder == "native":
+        # one process builds the directory, every process loads from it
+        from octex_b200 import index_dir
+        import shutil
+        path = os.path.join(args.index_dir, args.workload)
+        if local == 0:
+            shutil.rmtree(path, ignore_errors=True)
+            octex_b200.build_native(base, path, verbose=(rank == 0), **w["build"])
+        if world > 1:
+            dist.barrier()
+        host_arrays, meta = index_dir.read_index(path)
+        build_seconds = meta.get("build_seconds")
+        log(f"[rank {rank}] index directory ready in {time.time() - t0:.1f}s ({build_seconds})")
+        whole = octex_b200.load(path, devices=[local], placement="replicate")  # the whole index on this GPU
+        if sharded:
+            from octex_b200 import dist as odist
+            rows = args.placement == "shard-rows"
+            idx = octex_b200.load(path, devices=[local], placement="shard", rank=rank, world=world,
+                                  shard_vectors=rows, sketch="shard" if rows else "replicate")
+            odist.connect(idx)
+        else:
+            idx = whole
+        arrays = {"vectors": torch.as_tensor(np.asarray(host_arrays["vectors"]), device="cuda")}
+        index_bytes = sum(int(v.nbytes) for v in host_arrays.values())
     else:
-        idx = whole
-    index_bytes = sum(v.numel() * v.element_size() for v in arrays.values())
+        arrays, meta = build_index.build_arrays(base, build_index.IndexParams(**w["build"]),
+                                                device=f"cuda:{local}", keep_on_device=True,
+                                                verbose=(rank == 0))
+        torch.cuda.synchronize()
+        log(f"[rank {rank}] index built in {time.time() - t0:.1f}s")
+        whole = octex_b200.attach(arrays, meta, borrow=True)  # the whole index on this GPU
+        if sharded:
+            from octex_b200 import dist as odist
+            rows = args.placement == "shard-rows"
+            idx = octex_b200.attach(arrays, meta, borrow=False, rank=rank, world=world, placement="shard",
+                                    shard_vectors=rows, sketch="shard" if rows else "replicate")
+            odist.connect(idx)
+        else:
+            idx = whole
+        host_arrays = None
+        index_bytes = sum(v.numel() * v.element_size() for v in arrays.values())
     nq = len(queries)
     q_dev = torch.as_tensor(queries, device="cuda")
     truth = ground_truth(arrays["vectors"], q_dev, K)
@@ -549,7 +592,7 @@ def main():
         idx.set_projection(ordered=False)
         if rank == 0:
             from oracle import oracle_py
-            host = {k_: v.cpu().numpy() for k_, v in arrays.items()}
+            host = host_arrays if host_arrays is not None else {k_: v.cpu().numpy() for k_, v in arrays.items()}
             want_i, want_d, _ = oracle_py.Index(host, meta).search(queries[:ns], K, parts=world, **sp)
             multi["ids_match_checker_parts"] = float((want_i == i_s).mean())
             multi["dist_equal_checker_parts"] = bool(np.array_equal(want_d.view(np.uint32), d_s.view(np.uint32)))
@@ -607,7 +650,7 @@ def main():
                             "(NCCL send / receive), merge = their merge; round_rows = the wave of this "
                             "GPU's slice of the batch; gather_results = all-gather of the results")
     config = workload_config(args, w, sp, world)
-    config.update({"recall_at_10": rec, "recall_at_10_e2e": rec_e2e, "e2e_ids_equal_resident": e2e_same,
+    config.update({"builder": args.builder, "build_seconds": build_seconds, "recall_at_10": rec, "recall_at_10_e2e": rec_e2e, "e2e_ids_equal_resident": e2e_same,
                    "index_bytes": index_bytes, "l2": "flushed between timed steps (256 MB fill)",
                    "memory_report": idx.memory_report(),
                    "mean_per_query": {"levels_tried": float(stats[:, 0].mean()),
@@ -637,7 +680,7 @@ def main():
         host = None
         if not args.no_cpu_baseline:
             try:
-                host = {k_: v.cpu().numpy() for k_, v in arrays.items()}
+                host = host_arrays if host_arrays is not None else {k_: v.cpu().numpy() for k_, v in arrays.items()}
                 line["cpu_baseline"] = cpu_baseline(host, meta, queries, sp, args)
                 line["parity"] = parity_against_checker(idx, host, meta, queries, ids_run, dist_run, truth,
                                                         sp, args.cpu_sample)
@@ -646,8 +689,8 @@ def main():
                 line.setdefault("parity", {"error": str(e)})
         if not args.no_ref_kernels:
             try:
-                line["ref_kernels"] = reference_kernels(arrays, meta, idx, queries, ids_run, sp,
-                                                        kernel_ms, args.steps)
+                line["ref_kernels"] = reference_kernels(host_arrays if host_arrays is not None else arrays, meta,
+                                                        idx, queries, ids_run, sp, kernel_ms, args.steps)
             except Exception as e:
                 line["ref_kernels"] = {"error": str(e)}
     emit(line)

@@ -157,6 +157,13 @@ OCTEX_B200_EXPORT cuvsError_t cuvsOctexIndexGetDeviceBytes(cuvsOctexIndex_t inde
  * or from the Python tooling of this repository. */
 OCTEX_B200_EXPORT cuvsError_t cuvsOctexBuild(cuvsResources_t res, cuvsOctexIndexParams_t params,
                                              DLManagedTensor* dataset, const char* path);
+/* cuvsOctexBuild with plain pointers (the shape the Python layer calls): dataset [rows, dim]
+ * float32 (f16 = 0) or float16 (f16 = 1), row major, host or device memory; verbose = 1 prints
+ * progress on stderr (the reference's OCTEX_VERBOSE, cpp/src/neighbors/octex/detail/build_common.cuh:38-54). */
+OCTEX_B200_EXPORT cuvsError_t octexB200Build(cuvsResources_t res, cuvsOctexIndexParams_t params,
+                                             const void* dataset, int64_t rows, int64_t dim,
+                                             int32_t f16, int32_t verbose, const char* path);
+
 /* Load an index directory onto the GPU of this process into an empty handle (params NULL: the
  * defaults). octex.h:268-271 */
 OCTEX_B200_EXPORT cuvsError_t cuvsOctexLoad(cuvsResources_t res, const char* path,

@@ -50,6 +50,46 @@ struct search_params {
   bool use_graph       = true;
 };
 
+/// octex.hpp:32-92. The builder of this library makes member lists (the rows of a cell nearest its
+/// centre first, the reference's member_lists mode) and an exact neighbor table; the fields that
+/// choose among the reference's other build strategies (exact_lists, list_probes, member_lists,
+/// exact_table_max, table_passes, table_sketch_order, write_behind, devices) are accepted and have
+/// no effect.
+struct index_params {
+  int copies       = 200;   ///< random projections of the dataset
+  int blocks       = 4;     ///< E8 blocks per copy (8 coordinates each)
+  int pca_dims     = 64;    ///< principal directions a copy's projection is drawn from
+  std::vector<float> spacings{};  ///< lattice spacings, fine to coarse (empty: 2, 2.5, 3.2, 4, 5)
+  int list_len     = 64;    ///< rows listed per cell
+  int min_cell     = 1;     ///< cells with fewer rows are dropped (not at the coarsest spacing)
+  int log_buckets  = 20;    ///< log2 of the buckets the cells of a (copy, spacing) are hashed into
+  int sketch_width = 0;     ///< int8 sketch coordinates (0: chosen from the dimension)
+  int table_len    = 64;    ///< neighbors per row of the neighbor table (0: none)
+  bool reverse_edges = true;  ///< merge reverse edges into the table (half rule)
+  bool exact_lists = false, member_lists = false, table_sketch_order = false, write_behind = false;
+  int list_probes = 16, table_passes = 3;
+  int64_t exact_table_max = 20000000;
+  uint64_t seed = 0;
+  std::vector<int> devices{};
+  bool verbose = false;  ///< progress lines on stderr (the reference's OCTEX_VERBOSE)
+};
+
+/// The dataset of a build: n rows of dim float32 or float16 values, row major, in host or device
+/// memory (the two build overloads of octex.hpp:214-222 in one struct).
+struct build_dataset {
+  const void* data = nullptr;
+  bool f16         = false;
+  int64_t rows = 0, dim = 0;
+};
+
+/// Build an index of the dataset into the directory `path` (octex.hpp:214-222), on the current
+/// GPU. The directory is complete once its meta.json exists.
+void build(resources const& res, index_params const& params, build_dataset const& dataset,
+           std::string const& path);
+
+/// The sketch width the builder chooses for a dimension when index_params::sketch_width is 0.
+auto auto_sketch_width(int64_t dim) -> int;
+
 /// octex.hpp:138-143
 enum class placement : int { replicate = 0, shard = 1 };
 /// octex.hpp:146-153

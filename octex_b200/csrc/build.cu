@@ -16,6 +16,7 @@
 
 #include "e8.cuh"
 #include "npy.hpp"
+#include "sym_eigen.hpp"
 
 #include <cub/cub.cuh>
 
@@ -102,135 +103,6 @@ __global__ void __launch_bounds__(kScatterTile* kScatterTile)
     __syncthreads();
   }
   if (a0 + ta < D && b0 + tb < D) atomicAdd(&g[static_cast<int64_t>(a0 + ta) * D + b0 + tb], acc);
-}
-
-/// Eigenvalues (ascending) and eigenvectors (columns of v, stored row major [n, n]) of the
-/// symmetric matrix a [n, n] (destroyed): Householder reduction to tridiagonal form, then the QL
-/// algorithm with implicit shifts. Host code, fp64; n is a dimension (at most a few thousand).
-void symmetric_eigen(std::vector<double>& a, int n, std::vector<double>& d, std::vector<double>& v)
-{
-  std::vector<double> e(n, 0.0);
-  d.assign(n, 0.0);
-  auto A = [&](int i, int j) -> double& { return a[static_cast<size_t>(i) * n + j]; };
-  // reduction to tridiagonal form; a is overwritten with the orthogonal transformation
-  for (int i = n - 1; i > 0; i--) {
-    const int l = i - 1;
-    double h = 0.0, scale = 0.0;
-    if (l > 0) {
-      for (int k = 0; k <= l; k++)
-        scale += std::fabs(A(i, k));
-      if (scale == 0.0) {
-        e[i] = A(i, l);
-      } else {
-        for (int k = 0; k <= l; k++) {
-          A(i, k) /= scale;
-          h += A(i, k) * A(i, k);
-        }
-        double f = A(i, l);
-        double g = f >= 0.0 ? -std::sqrt(h) : std::sqrt(h);
-        e[i]     = scale * g;
-        h -= f * g;
-        A(i, l) = f - g;
-        f       = 0.0;
-        for (int j = 0; j <= l; j++) {
-          A(j, i) = A(i, j) / h;
-          g       = 0.0;
-          for (int k = 0; k <= j; k++)
-            g += A(j, k) * A(i, k);
-          for (int k = j + 1; k <= l; k++)
-            g += A(k, j) * A(i, k);
-          e[j] = g / h;
-          f += e[j] * A(i, j);
-        }
-        const double hh = f / (h + h);
-        for (int j = 0; j <= l; j++) {
-          f    = A(i, j);
-          e[j] = g = e[j] - hh * f;
-          for (int k = 0; k <= j; k++)
-            A(j, k) -= f * e[k] + g * A(i, k);
-        }
-      }
-    } else {
-      e[i] = A(i, l);
-    }
-    d[i] = h;
-  }
-  d[0] = 0.0;
-  e[0] = 0.0;
-  for (int i = 0; i < n; i++) {
-    const int l = i - 1;
-    if (d[i] != 0.0) {
-      for (int j = 0; j <= l; j++) {
-        double g = 0.0;
-        for (int k = 0; k <= l; k++)
-          g += A(i, k) * A(k, j);
-        for (int k = 0; k <= l; k++)
-          A(k, j) -= g * A(k, i);
-      }
-    }
-    d[i]    = A(i, i);
-    A(i, i) = 1.0;
-    for (int j = 0; j <= l; j++)
-      A(j, i) = A(i, j) = 0.0;
-  }
-  // QL with implicit shifts on (d, e); the transformation accumulates in a
-  for (int i = 1; i < n; i++)
-    e[i - 1] = e[i];
-  e[n - 1] = 0.0;
-  for (int l = 0; l < n; l++) {
-    int iter = 0, m;
-    do {
-      for (m = l; m < n - 1; m++) {
-        const double dd = std::fabs(d[m]) + std::fabs(d[m + 1]);
-        if (std::fabs(e[m]) <= 2.3e-16 * dd) break;
-      }
-      if (m != l) {
-        OCTEX_EXPECTS(iter++ < 200, "octex: the eigenvalue iteration of the sample PCA did not converge");
-        double g = (d[l + 1] - d[l]) / (2.0 * e[l]);
-        double r = std::hypot(g, 1.0);
-        g        = d[m] - d[l] + e[l] / (g + (g >= 0.0 ? std::fabs(r) : -std::fabs(r)));
-        double s = 1.0, c = 1.0, p = 0.0;
-        int i;
-        for (i = m - 1; i >= l; i--) {
-          double f = s * e[i], b = c * e[i];
-          e[i + 1] = r = std::hypot(f, g);
-          if (r == 0.0) {
-            d[i + 1] -= p;
-            e[m] = 0.0;
-            break;
-          }
-          s        = f / r;
-          c        = g / r;
-          g        = d[i + 1] - p;
-          r        = (d[i] - g) * s + 2.0 * c * b;
-          d[i + 1] = g + (p = s * r);
-          g        = c * r - b;
-          for (int k = 0; k < n; k++) {
-            f           = A(k, i + 1);
-            A(k, i + 1) = s * A(k, i) + c * f;
-            A(k, i)     = c * A(k, i) - s * f;
-          }
-        }
-        if (r == 0.0 && i >= l) continue;
-        d[l] -= p;
-        e[l] = g;
-        e[m] = 0.0;
-      }
-    } while (m != l);
-  }
-  // ascending order
-  std::vector<int> order(n);
-  for (int i = 0; i < n; i++)
-    order[i] = i;
-  std::sort(order.begin(), order.end(), [&](int x, int y) { return d[x] < d[y]; });
-  std::vector<double> ds(n);
-  v.assign(static_cast<size_t>(n) * n, 0.0);
-  for (int j = 0; j < n; j++) {
-    ds[j] = d[order[j]];
-    for (int k = 0; k < n; k++)
-      v[static_cast<size_t>(k) * n + j] = A(k, order[j]);
-  }
-  d.swap(ds);
 }
 
 struct pca_result {
@@ -595,6 +467,7 @@ void cells_of_copy(cell_scratch& sc, const __half* x, const float* mean, const f
     cub::DeviceScan::ExclusiveSum(sc.tmp.ptr, tb, sc.pop.as<int32_t>(), sc.start.as<int32_t>(), runs, s);
     // the kept cells: all at the coarsest spacing, else those of at least min_cell rows
     const bool filter = params.min_cell > 1 && j < L - 1;
+    OCTEX_EXPECTS(runs > 0, "octex: a spacing of a copy produced no cell at all");
     keep_kernel<<<grid_for(runs, 256), 256, 0, s>>>(sc.pop.as<int32_t>(), runs, filter ? params.min_cell : 0,
                                                     sc.keep.as<int32_t>());
     tb = sc.tmp_bytes;
@@ -606,21 +479,24 @@ void cells_of_copy(cell_scratch& sc, const __half* x, const float* mean, const f
       OCTEX_CUDA_TRY(cudaStreamSynchronize(s));
     }
     const int64_t cells = static_cast<int64_t>(last_slot) + last_keep;
-    compact_cells_kernel<<<grid_for(runs, 256), 256, 0, s>>>(
+    if (runs > 0)
+      compact_cells_kernel<<<grid_for(runs, 256), 256, 0, s>>>(
       sc.ukey.as<long long>(), sc.start.as<int32_t>(), sc.pop.as<int32_t>(), sc.keep.as<int32_t>(),
       sc.slot.as<int32_t>(), runs, sc.key.as<long long>(), sc.kstart.as<int32_t>(), sc.kpop.as<int32_t>());
     // (bucket, code) order of the cells and the bucket bounds (build_cells.cuh:387-449): the cells
     // are in code order already and the sort by bucket is stable
-    bucket_kernel<<<grid_for(cells, 256), 256, 0, s>>>(sc.key.as<long long>(), cells, T - 1, sc.bucket.as<int32_t>());
-    iota_kernel<<<grid_for(cells, 256), 256, 0, s>>>(sc.perm.as<int32_t>(), cells);
-    tb = sc.tmp_bytes;
-    cub::DeviceRadixSort::SortPairs(sc.tmp.ptr, tb, sc.bucket.as<int32_t>(), sc.bucket_alt.as<int32_t>(),
-                                    sc.perm.as<int32_t>(), sc.perm_alt.as<int32_t>(), cells, 0, params.log_buckets, s);
-    gather_kernel<long long><<<grid_for(cells, 256), 256, 0, s>>>(sc.key.as<long long>(), sc.perm_alt.as<int32_t>(),
-                                                                 cells, sc.skeys.as<long long>());
-    cell_lists_kernel<<<grid_for(cells * l, 256), 256, 0, s>>>(sc.rows.as<int32_t>(), sc.kstart.as<int32_t>(),
-                                                               sc.kpop.as<int32_t>(), sc.perm_alt.as<int32_t>(), cells,
-                                                               l, sc.lists.as<int32_t>());
+    if (cells > 0) {
+      bucket_kernel<<<grid_for(cells, 256), 256, 0, s>>>(sc.key.as<long long>(), cells, T - 1, sc.bucket.as<int32_t>());
+      iota_kernel<<<grid_for(cells, 256), 256, 0, s>>>(sc.perm.as<int32_t>(), cells);
+      tb = sc.tmp_bytes;
+      cub::DeviceRadixSort::SortPairs(sc.tmp.ptr, tb, sc.bucket.as<int32_t>(), sc.bucket_alt.as<int32_t>(),
+                                      sc.perm.as<int32_t>(), sc.perm_alt.as<int32_t>(), cells, 0, params.log_buckets, s);
+      gather_kernel<long long><<<grid_for(cells, 256), 256, 0, s>>>(sc.key.as<long long>(), sc.perm_alt.as<int32_t>(),
+                                                                   cells, sc.skeys.as<long long>());
+      cell_lists_kernel<<<grid_for(cells * l, 256), 256, 0, s>>>(sc.rows.as<int32_t>(), sc.kstart.as<int32_t>(),
+                                                                 sc.kpop.as<int32_t>(), sc.perm_alt.as<int32_t>(), cells,
+                                                                 l, sc.lists.as<int32_t>());
+    }
     bucket_bounds_kernel<<<grid_for(T1, 256), 256, 0, s>>>(sc.bucket_alt.as<int32_t>(), cells, T1,
                                                            sc.offsets.as<int32_t>());
     OCTEX_CUDA_TRY(cudaPeekAtLastError());
@@ -819,7 +695,7 @@ __global__ void __launch_bounds__(128)
   const int64_t v = static_cast<int64_t>(blockIdx.x) * 4 + warp;
   if (v >= n) return;
   const int64_t e0 = efirst[v], e1 = efirst[v + 1];
-  const int nrev   = static_cast<int>(min<int64_t>(e1 - e0, h));
+  const int nrev   = static_cast<int>(min(e1 - e0, static_cast<int64_t>(h)));
   const int total  = k + nrev;  // forward neighbors (self already dropped): k of them at most
   for (int t = lane; t < total; t += 32) {
     int32_t id;

@@ -4,6 +4,7 @@
 // exception becomes CUVS_ERROR plus a per-thread message, cleared on success; argument checks
 // that need no GPU work with res == 0.
 
+#include "build.hpp"
 #include "search_impl.hpp"
 
 #include <octex_b200.h>
@@ -309,16 +310,62 @@ cuvsError_t cuvsOctexIndexGetDeviceBytes(cuvsOctexIndex_t index, int64_t* bytes)
 cuvsError_t cuvsOctexBuild(cuvsResources_t res, cuvsOctexIndexParams_t params,
                            DLManagedTensor* dataset, const char* path)
 {
-  (void)res;
   return translate([=] {
     OCTEX_EXPECTS(path != nullptr, "octex: the index directory is NULL");
     OCTEX_EXPECTS(params != nullptr && dataset != nullptr, "octex: a build argument is NULL");
-    const auto dtype = dataset->dl_tensor.dtype;
-    OCTEX_EXPECTS(dtype.code == kDLFloat && (dtype.bits == 32 || dtype.bits == 16),
+    DLTensor const& t = dataset->dl_tensor;
+    OCTEX_EXPECTS(t.dtype.code == kDLFloat && (t.dtype.bits == 32 || t.dtype.bits == 16) && t.dtype.lanes == 1,
                   "octex: the dataset must be float32 or float16");
-    throw octex_b200::error(
-      "octex: this library covers the search path; build the index directory with the reference's "
-      "builder or with octex_b200.build_index");
+    OCTEX_EXPECTS(t.ndim == 2, "octex: the DLPack tensor has the wrong number of dimensions");
+    if (t.strides != nullptr)
+      OCTEX_EXPECTS((t.shape[1] == 1 || t.strides[1] == 1) && (t.shape[0] == 1 || t.strides[0] == t.shape[1]),
+                    "octex: the DLPack tensor must be dense and row major");
+    octex_b200::index_params p;
+    p.copies = params->copies, p.blocks = params->blocks, p.pca_dims = params->pca_dims;
+    if (params->spacings != nullptr && params->n_spacings > 0)
+      p.spacings.assign(params->spacings, params->spacings + params->n_spacings);
+    p.list_len = params->list_len, p.min_cell = params->min_cell, p.log_buckets = params->log_buckets;
+    p.sketch_width = params->sketch_width, p.table_len = params->table_len;
+    p.reverse_edges = params->reverse_edges, p.seed = params->seed;
+    p.exact_lists = params->exact_lists, p.list_probes = params->list_probes, p.member_lists = params->member_lists;
+    p.exact_table_max = params->exact_table_max, p.table_passes = params->table_passes;
+    p.table_sketch_order = params->table_sketch_order, p.write_behind = params->write_behind;
+    if (params->devices != nullptr && params->n_devices > 0)
+      p.devices.assign(params->devices, params->devices + params->n_devices);
+    OCTEX_EXPECTS(p.devices.size() <= 1, "octex: this builder works on one GPU (index_params::devices names several)");
+    int cur = 0;
+    OCTEX_CUDA_TRY(cudaGetDevice(&cur));
+    if (!p.devices.empty()) OCTEX_CUDA_TRY(cudaSetDevice(p.devices[0]));
+    octex_b200::build_dataset d;
+    d.data = static_cast<const char*>(t.data) + t.byte_offset;
+    d.f16  = t.dtype.bits == 16;
+    d.rows = t.shape[0], d.dim = t.shape[1];
+    try {
+      octex_b200::build(as_res(res), p, d, std::string(path));
+    } catch (...) {
+      cudaSetDevice(cur);
+      throw;
+    }
+    OCTEX_CUDA_TRY(cudaSetDevice(cur));
+  });
+}
+
+cuvsError_t octexB200Build(cuvsResources_t res, cuvsOctexIndexParams_t params, const void* dataset,
+                           int64_t rows, int64_t dim, int32_t f16, int32_t verbose, const char* path)
+{
+  return translate([=] {
+    OCTEX_EXPECTS(path != nullptr && params != nullptr && dataset != nullptr, "octex: a build argument is NULL");
+    octex_b200::index_params p;
+    p.copies = params->copies, p.blocks = params->blocks, p.pca_dims = params->pca_dims;
+    if (params->spacings != nullptr && params->n_spacings > 0)
+      p.spacings.assign(params->spacings, params->spacings + params->n_spacings);
+    p.list_len = params->list_len, p.min_cell = params->min_cell, p.log_buckets = params->log_buckets;
+    p.sketch_width = params->sketch_width, p.table_len = params->table_len;
+    p.reverse_edges = params->reverse_edges, p.seed = params->seed;
+    p.verbose = verbose != 0;
+    octex_b200::build_dataset d;
+    d.data = dataset, d.f16 = f16 != 0, d.rows = rows, d.dim = dim;
+    octex_b200::build(as_res(res), p, d, std::string(path));
   });
 }
 

@@ -416,9 +416,10 @@ def build(dataset, path=None, *, metric="sqeuclidean", placement="shard", vector
     lives as long as the returned index (``Index.save`` keeps it).  Keyword arguments are the
     fields of ``index_params``; ``devices`` selects the GPU the index is loaded on.
 
-    The builder behind this call is this package's tooling (``octex_b200.build_index``: exact member
-    lists and an exact neighbor table, on the GPU when there is one), meant for data of up to a few
-    million rows; it writes the reference's directory format."""
+    With a GPU the library's own builder makes the directory (``octexB200Build``: member lists and
+    an exact neighbor table, CUDA kernels on the current device); without one, the package's
+    tooling (``octex_b200.build_index``, torch on the CPU) writes the same format for small
+    data."""
     from . import build_index
     check_metric(metric)
     unknown = set(index_params) - set(INDEX_PARAMS)
@@ -440,13 +441,67 @@ def build(dataset, path=None, *, metric="sqeuclidean", placement="shard", vector
         path = tmp.name
     path = os.fspath(path)
     os.makedirs(path, exist_ok=True)
-    device = "cuda" if torch is not None and torch.cuda.is_available() else "cpu"
-    build_index.build(data, path, build_index.IndexParams(**fields), device=device)
+    if torch is not None and torch.cuda.is_available():
+        build_native(data, path, **fields)
+    else:
+        build_index.build(data, path, build_index.IndexParams(**fields), device="cpu")
     idx = load(path, devices=index_params.get("devices"), placement=placement,
                vectors_on_host=vectors_on_host, table_on_host=table_on_host,
                shard_vectors=shard_vectors, sketch=sketch)
     idx._tmpdir = tmp
     return idx
+
+
+def index_params(**kw):
+    """(struct cuvsOctexIndexParams with the defaults of the C++ API, then ``kw``; keep-alive)."""
+    unknown = set(kw) - set(INDEX_PARAMS)
+    if unknown:
+        raise TypeError(f"octex: unknown index parameters {sorted(unknown)}")
+    pp = C.POINTER(_lib.IndexParams)()
+    _lib.check(_lib.lib().cuvsOctexIndexParamsCreate(C.byref(pp)))
+    p = _lib.IndexParams()
+    C.memmove(C.byref(p), pp, C.sizeof(p))
+    _lib.check(_lib.lib().cuvsOctexIndexParamsDestroy(pp))
+    keep = []
+    for name, value in kw.items():
+        if value is None:
+            continue
+        if name == "spacings":
+            arr = (C.c_float * len(value))(*[float(f) for f in value])
+            keep.append(arr)
+            p.spacings, p.n_spacings = C.cast(arr, C.POINTER(C.c_float)), len(value)
+        elif name == "devices":
+            devs = [int(v) for v in ([value] if isinstance(value, int) else value)]
+            arr = (C.c_int32 * len(devs))(*devs)
+            keep.append(arr)
+            p.devices, p.n_devices = C.cast(arr, C.POINTER(C.c_int32)), len(devs)
+        else:
+            setattr(p, name, value)
+    return p, keep
+
+
+def build_native(dataset, path, verbose=False, **params):
+    """Build an index directory at ``path`` with the library's own GPU builder
+    (``octexB200Build``).  ``dataset`` [n, dim]: float32 or float16, numpy or torch, host or
+    device memory."""
+    data, _ = adopt(dataset)
+    if _is_torch(data):
+        data = data.detach().contiguous()
+        kind, ptr = str(data.dtype).replace("torch.", ""), data.data_ptr()
+    else:
+        data = np.ascontiguousarray(data)
+        kind, ptr = str(data.dtype), data.ctypes.data
+    if kind not in ("float32", "float16"):
+        raise TypeError("octex: dataset must be float32 or float16")
+    if len(data.shape) != 2:
+        raise ValueError("octex: dataset must be a matrix [n, dim]")
+    p, keep = index_params(**params)
+    os.makedirs(os.fspath(path), exist_ok=True)
+    _lib.check(_lib.lib().octexB200Build(
+        C.c_size_t(0), C.byref(p), C.c_void_p(ptr), C.c_int64(data.shape[0]), C.c_int64(data.shape[1]),
+        C.c_int32(1 if kind == "float16" else 0), C.c_int32(int(verbose)), os.fspath(path).encode()))
+    del keep
+    return os.fspath(path)
 
 
 def _address(a):

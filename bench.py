@@ -63,6 +63,11 @@ WORKLOADS = {
         gen="global_descriptor_like", n=1_000_000, dim=960, nq=1_000,
         build=dict(copies=96, blocks=4, pca_dims=64, list_len=64, min_cell=16, log_buckets=20,
                    sketch_width=128, table_len=64)),
+    # BASELINE.json config 4: 10 M embedding-like rows (shard placement with --gpus 2/4/8)
+    "embedding-10m": dict(
+        gen="embedding_like", n=10_000_000, dim=96, nq=10_000,
+        build=dict(copies=64, blocks=4, pca_dims=64, list_len=32, min_cell=16, log_buckets=20,
+                   sketch_width=64, table_len=64)),
 }
 LADDER = [
     dict(read=16, starts=32, waves=1, rerank=128, wave_rerank=384),
@@ -75,6 +80,8 @@ LADDER = [
     dict(read=32, starts=192, waves=3, rerank=384, wave_rerank=384),
     dict(read=32, starts=256, waves=3, rerank=512, wave_rerank=512),
     dict(read=32, starts=256, waves=4, rerank=512, wave_rerank=512),
+    dict(read=32, starts=384, waves=4, rerank=512, wave_rerank=512),
+    dict(read=64, starts=512, waves=4, rerank=512, wave_rerank=512),
 ]
 
 
@@ -206,15 +213,23 @@ def make_data(w, rank_seed):
     return base, queries
 
 
-def ground_truth(vectors16, queries_t, k):
+def ground_truth(vectors16, queries_t, k, rows_at_once=1 << 19):
+    """Exact k nearest stored rows of every query (fp32 arithmetic on the GPU, in blocks of rows)."""
     import torch
-    v = vectors16.float()
-    vn = (v * v).sum(1)
     out = []
     for q0 in range(0, queries_t.shape[0], 2048):
         q = queries_t[q0:q0 + 2048]
-        d = vn[None, :] - 2.0 * (q @ v.T)
-        out.append(d.topk(k, dim=1, largest=False).indices)
+        best_d = best_i = None
+        for r0 in range(0, vectors16.shape[0], rows_at_once):
+            v = vectors16[r0:r0 + rows_at_once].float()
+            d, i = ((v * v).sum(1)[None, :] - 2.0 * (q @ v.T)).topk(min(k, v.shape[0]), dim=1, largest=False)
+            i = i + r0
+            if best_d is not None:
+                d, i = torch.cat([best_d, d], 1), torch.cat([best_i, i], 1)
+                d, at = d.topk(k, dim=1, largest=False)
+                i = i.gather(1, at)
+            best_d, best_i = d, i
+        out.append(best_i)
     return torch.cat(out).cpu().numpy()
 
 

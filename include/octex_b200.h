@@ -164,6 +164,17 @@ OCTEX_B200_EXPORT cuvsError_t octexB200Build(cuvsResources_t res, cuvsOctexIndex
                                              const void* dataset, int64_t rows, int64_t dim,
                                              int32_t f16, int32_t verbose, const char* path);
 
+/* Exact k nearest other rows of every row of rows_f16 [n, dim] (fp16, device memory of the current
+ * GPU) by squared L2 between the fp16 rows: what the builder's neighbor table starts from (the
+ * reference calls cuVS brute force there, cpp/src/neighbors/octex/detail/build_table.cuh:60-142).
+ * ids int32 / distances float [n, k] in device memory: nearest first, equal distances by ascending
+ * id, -1 / +inf where a row has fewer than k others. method 0: tensor cores when dim is a multiple
+ * of 8 and k <= 120, else the plain scan; 1: tensor cores or an error; 2: the plain scan. Returns
+ * when the work on the resources' stream is done. */
+OCTEX_B200_EXPORT cuvsError_t octexB200ExactNeighbors(cuvsResources_t res, const void* rows_f16, int64_t n,
+                                                      int32_t dim, int32_t k, int32_t method, int32_t* ids,
+                                                      float* distances);
+
 /* Load an index directory onto the GPU of this process into an empty handle (params NULL: the
  * defaults). octex.h:268-271 */
 OCTEX_B200_EXPORT cuvsError_t cuvsOctexLoad(cuvsResources_t res, const char* path,

@@ -5,9 +5,9 @@ queries; ``build`` makes an index directory on the GPU.  ``build_index`` (a torc
 the builder that also runs on a CPU) and ``synth`` (seeded synthetic data) are tooling.
 The CUDA library is ``octex_b200/lib/liboctex_b200.so``; without it nothing here computes.
 """
-from .index import (Index, attach, build, build_native, cell_codes, index_params, load,  # noqa: F401
-                    load_params, search_params, stored_vectors)
+from .index import (Index, attach, build, build_native, cell_codes, exact_neighbors,  # noqa: F401
+                    index_params, load, load_params, search_params, stored_vectors)
 
 __version__ = "0.1.0"
-__all__ = ["Index", "attach", "build", "build_native", "cell_codes", "index_params", "load",
+__all__ = ["Index", "attach", "build", "build_native", "cell_codes", "exact_neighbors", "index_params", "load",
            "load_params", "search_params", "stored_vectors", "__version__"]

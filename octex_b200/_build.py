@@ -10,7 +10,7 @@ _ROOT = os.path.dirname(_PKG)
 CSRC = os.path.join(_PKG, "csrc")
 LIB_DIR = os.path.join(_PKG, "lib")
 LIB = os.path.join(LIB_DIR, "liboctex_b200.so")
-SOURCES = ["prep.cu", "round.cu", "project_tc.cu", "load.cu", "search.cu", "c_api.cu",
+SOURCES = ["prep.cu", "round.cu", "project_tc.cu", "knn_tc.cu", "load.cu", "search.cu", "c_api.cu",
            "static_scratch.cu", "comm.cu", "build.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC,-fvisibility=hidden", "-I", os.path.join(_ROOT, "include"),

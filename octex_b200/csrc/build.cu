@@ -18,6 +18,8 @@
 #include "npy.hpp"
 #include "sym_eigen.hpp"
 
+#include "kernels.hpp"
+
 #include <cub/cub.cuh>
 
 #include <algorithm>
@@ -754,6 +756,38 @@ __global__ void __launch_bounds__(128)
     table[v * k + t] = -1;
 }
 
+}  // namespace
+
+void exact_neighbors(const __half* x, int64_t n, int D, int K, int method, int32_t* ids, float* dist, cudaStream_t s)
+{
+  OCTEX_EXPECTS(n > 0 && D > 0 && K > 0, "octex: exact_neighbors needs rows, a dimension and K >= 1");
+  OCTEX_EXPECTS(method >= 0 && method <= 2, "octex: exact_neighbors method is 0 (choose), 1 (tensor cores) or 2 (plain)");
+  int dev = 0;
+  OCTEX_CUDA_TRY(cudaGetDevice(&dev));
+  dbuf norm(dev, sizeof(float) * n);
+  row_norms_kernel<<<grid_for(n, 128), 128, 0, s>>>(x, n, D, norm.as<float>());
+  const bool covered = kernels::knn_tc_supported(n, D, K);
+  OCTEX_EXPECTS(method != 1 || covered,
+                "octex: the tensor-core neighbor scan needs a dimension that is a multiple of 8 and K <= 120");
+  if (method == 1 || (method == 0 && covered)) {
+    dbuf error(dev, sizeof(int));
+    OCTEX_CUDA_TRY(cudaMemsetAsync(error.ptr, 0, sizeof(int), s));
+    kernels::knn_tc(x, norm.as<float>(), n, D, K, 0, n, ids, dist, error.as<int>(), s);
+    OCTEX_CUDA_TRY(cudaPeekAtLastError());
+    const int gave_up = to_host<int>(error.ptr, 1)[0];
+    OCTEX_EXPECTS(gave_up == 0, "octex: the neighbor scan gave up waiting inside the kernel (code " +
+                                  std::to_string(gave_up) + "); its lists are incomplete");
+  } else {
+    const size_t smem = sizeof(float) * (2 * kKnnDim * (kKnnTile + 4) + kKnnTile * (kKnnTile + 1));
+    OCTEX_CUDA_TRY(cudaFuncSetAttribute(knn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    knn_kernel<<<grid_for(n, kKnnTile), 256, smem, s>>>(x, norm.as<float>(), n, D, K, 0, n, ids, dist);
+    OCTEX_CUDA_TRY(cudaPeekAtLastError());
+  }
+  OCTEX_CUDA_TRY(cudaStreamSynchronize(s));
+}
+
+namespace {
+
 // ---- the directory ---------------------------------------------------------------------------------
 
 /// A .npy file (format 1.0, little endian, C order, header padded to 64 bytes) written in pieces.
@@ -946,13 +980,9 @@ void build(resources const& res, index_params const& given, build_dataset const&
   const int k = params.table_len;
   if (k > 0) {
     const int K = k;  // self is excluded inside the scan
-    dbuf norm(dev, sizeof(float) * n), fwd(dev, sizeof(int32_t) * n * K), fd(dev, sizeof(float) * n * K);
-    row_norms_kernel<<<grid_for(n, 128), 128, 0, s>>>(x16.as<__half>(), n, D, norm.as<float>());
-    const size_t smem = sizeof(float) * (2 * kKnnDim * (kKnnTile + 4) + kKnnTile * (kKnnTile + 1));
-    OCTEX_CUDA_TRY(cudaFuncSetAttribute(knn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    knn_kernel<<<grid_for(n, kKnnTile), 256, smem, s>>>(x16.as<__half>(), norm.as<float>(), n, D, K, 0, n,
-                                                        fwd.as<int32_t>(), fd.as<float>());
-    OCTEX_CUDA_TRY(cudaPeekAtLastError());
+    dbuf fwd(dev, sizeof(int32_t) * n * K), fd(dev, sizeof(float) * n * K);
+    exact_neighbors(x16.as<__half>(), n, D, K, 0, fwd.as<int32_t>(), fd.as<float>(), s);
+    took.emplace_back("table_scan", seconds_since(t0));
     dbuf out(dev, sizeof(int32_t) * n * k);
     const int h = std::max(1, k / 2);
     if (params.reverse_edges) {

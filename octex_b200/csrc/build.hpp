@@ -6,6 +6,9 @@
 
 #include <octex_b200.hpp>
 
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
 #include <string>
 #include <sys/stat.h>
 
@@ -26,5 +29,12 @@ inline void make_directory(std::string const& path)
   struct stat st {};
   OCTEX_EXPECTS(::stat(path.c_str(), &st) == 0 && S_ISDIR(st.st_mode), "octex: " + path + " is not a directory");
 }
+
+/// The K nearest other rows of every row of x f16 [n, D] (device memory, current device) by
+/// squared distance between the fp16 rows: ids i32 / dist f32 [n, K] in device memory, nearest
+/// first, equal distances by ascending id, -1 / +inf where a row has fewer than K others.
+/// method 0 picks the tensor-core scan when it covers the shape, 1 asks for it, 2 for the plain one.
+/// Returns after the stream has finished.
+void exact_neighbors(const __half* x, int64_t n, int D, int K, int method, int32_t* ids, float* dist, cudaStream_t s);
 
 }  // namespace octex_b200

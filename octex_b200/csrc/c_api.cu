@@ -369,6 +369,16 @@ cuvsError_t octexB200Build(cuvsResources_t res, cuvsOctexIndexParams_t params, c
   });
 }
 
+cuvsError_t octexB200ExactNeighbors(cuvsResources_t res, const void* rows_f16, int64_t n, int32_t dim, int32_t k,
+                                    int32_t method, int32_t* ids, float* distances)
+{
+  return translate([=] {
+    OCTEX_EXPECTS(rows_f16 != nullptr && ids != nullptr && distances != nullptr, "octex: an argument is NULL");
+    octex_b200::exact_neighbors(static_cast<const __half*>(rows_f16), n, dim, k, method, ids, distances,
+                                as_res(res).stream);
+  });
+}
+
 cuvsError_t cuvsOctexLoad(cuvsResources_t res, const char* path, cuvsOctexLoadParams_t params,
                           cuvsOctexIndex_t index)
 {

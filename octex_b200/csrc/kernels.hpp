@@ -202,4 +202,13 @@ void final_rerank(const long long* si, int KO, int R, const __half* vectors, row
 void merge_kept(const long long* src_i, const float* src_d, int nsrc, int64_t src_stride, int KO,
                 int P, int m, long long* si, float* sd, cudaStream_t s);
 
+/// Exact K nearest rows (self excluded) of the rows [q_first, q_first + q_count) of x f16 [n, D]
+/// among all n rows, by |a|^2 + |b|^2 - 2 a.b with the dot products on the tensor cores
+/// (knn_tc.cu); norm f32 [n] = |x_r|^2. best_id i32 / best_d f32 [q_count, K], nearest first,
+/// equal distances by ascending id, -1 / +inf padded. *error (device word, zero on entry) is set
+/// when a wait inside the kernel ran out; the lists are then incomplete.
+bool knn_tc_supported(int64_t n, int D, int K);
+void knn_tc(const __half* x, const float* norm, int64_t n, int D, int K, int64_t q_first, int64_t q_count,
+            int32_t* best_id, float* best_d, int* error, cudaStream_t s);
+
 }  // namespace octex_b200::kernels

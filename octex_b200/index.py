@@ -504,6 +504,27 @@ def build_native(dataset, path, verbose=False, **params):
     return os.fspath(path)
 
 
+def exact_neighbors(rows, k, method="auto"):
+    """The ``k`` nearest other rows of every row of ``rows`` [n, dim] (a torch CUDA tensor, used as
+    float16) by squared L2: ``(ids int32 [n, k], distances float32 [n, k])`` as torch tensors on the
+    same GPU, nearest first (``octexB200ExactNeighbors``).  ``method``: "auto", "tensor" (the
+    tcgen05 scan; dim a multiple of 8, k <= 120) or "plain"."""
+    torch = _torch()
+    if not (_is_torch(rows) and rows.is_cuda and rows.dim() == 2):
+        raise TypeError("octex: exact_neighbors takes a torch CUDA matrix [n, dim]")
+    x = rows.detach().to(torch.float16).contiguous()
+    n, dim = x.shape
+    ids = torch.empty((n, int(k)), dtype=torch.int32, device=x.device)
+    dist = torch.empty((n, int(k)), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        torch.cuda.current_stream().synchronize()
+        _lib.check(_lib.lib().octexB200ExactNeighbors(
+            C.c_size_t(0), C.c_void_p(x.data_ptr()), C.c_int64(n), C.c_int32(dim), C.c_int32(int(k)),
+            C.c_int32({"auto": 0, "tensor": 1, "plain": 2}[method]), C.c_void_p(ids.data_ptr()),
+            C.c_void_p(dist.data_ptr())))
+    return ids, dist
+
+
 def _address(a):
     if a is None:
         return None

@@ -184,3 +184,35 @@ def test_build_through_the_reference_call(tmp_path):
     d, i = idx.search(base[:50], 5, read=8, starts=16, waves=1)
     assert (i[:, 0] == np.arange(50)).mean() > 0.9  # a row's nearest neighbor is itself
     idx.close()
+
+
+@pytest.mark.parametrize("n,dim,k", [(3000, 96, 24), (1000, 128, 64), (777, 32, 120), (2500, 960, 16), (130, 8, 7)])
+def test_tensor_core_neighbor_scan(n, dim, k):
+    """octexB200ExactNeighbors: the tcgen05 scan against the plain scan and against float64 brute
+    force over the same fp16 rows (ragged last tiles, one to fifteen 64-wide steps of the dimension,
+    short and long lists, more rows asked for than some tiles hold)."""
+    import torch
+    from octex_b200 import synth
+    x = torch.as_tensor(synth.plumbing(n, dim, seed=11), device="cuda").half()
+    ids_t, d_t = octex_b200.exact_neighbors(x, k, method="tensor")
+    ids_p, d_p = octex_b200.exact_neighbors(x, k, method="plain")
+    ids_t, d_t, ids_p, d_p = (a.cpu().numpy() for a in (ids_t, d_t, ids_p, d_p))
+    xf = x.double().cpu().numpy()
+    g = xf @ xf.T
+    sq = np.diag(g)
+    full = sq[:, None] + sq[None, :] - 2 * g
+    np.fill_diagonal(full, np.inf)
+    order = np.argsort(full, axis=1, kind="stable")[:, :k]
+    want_d = np.take_along_axis(full, order, axis=1)
+    for ids, d in ((ids_t, d_t), (ids_p, d_p)):
+        assert (ids >= 0).all() and (ids != np.arange(n)[:, None]).all()
+        assert all(len(set(r.tolist())) == k for r in ids)
+        assert (np.diff(d, axis=1) >= 0).all()                       # nearest first
+        # the distances are those of the named rows, and as small as the exact ones, up to fp32
+        # rounding of |a|^2 + |b|^2 - 2 a.b
+        scale = 1e-3 * (1 + sq.max())
+        assert np.abs(np.take_along_axis(full, ids.astype(np.int64), axis=1) - d).max() < scale
+        assert np.abs(d - want_d).max() < scale
+    # both scans find the same rows but for near-ties
+    same = np.mean([len(set(a.tolist()) & set(b.tolist())) / k for a, b in zip(ids_t, ids_p)])
+    assert same > 0.999, same

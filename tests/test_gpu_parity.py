@@ -398,6 +398,7 @@ FUSED_SETS = [
     dict(read=16, starts=32, waves=1, rerank=128, wave_rerank=384),
     dict(read=8, starts=24, waves=2, rerank=64, wave_rerank=100),
     dict(read=32, starts=128, waves=2, rerank=256, wave_rerank=256),
+    dict(read=32, starts=256, waves=2, rerank=256, wave_rerank=256),
     dict(read=8, starts=64, waves=1, sketch_rank=True, final_rerank=32),
 ]
 

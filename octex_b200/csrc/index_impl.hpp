@@ -70,6 +70,7 @@ struct device_part {
   dbuf sketch_norm;                      // f32 [n]: sum_k (code_k scale_k)^2 of every sketch row
   dealt_rows table_rows, sketch_rows, vector_rows;
   cudaStream_t stream = nullptr;
+  cudaStream_t second = nullptr;  // created when a search first alternates its batches between two streams
   int64_t bytes       = 0;
 
   device_part() = default;
@@ -85,6 +86,7 @@ struct device_part {
       for (void* p : d->opened)
         cudaIpcCloseMemHandle(p);
     if (stream != nullptr) cudaStreamDestroy(stream);
+    if (second != nullptr) cudaStreamDestroy(second);
     cudaSetDevice(cur);
   }
 };

@@ -493,7 +493,7 @@ auto make_plan(index_impl& ix, search_params const& sp, int m, int k, debug_opti
   return plp;
 }
 
-auto get_plan(index_impl& ix, search_params const& sp, int m, int k) -> std::shared_ptr<plan>
+auto get_plan(index_impl& ix, search_params const& sp, int m, int k, int lane) -> std::shared_ptr<plan>
 {
   const debug_options dbg = ix_debug(ix);
   std::string key = std::to_string(m) + "/" + std::to_string(k) + "/" + std::to_string(sp.read) +
@@ -503,13 +503,18 @@ auto get_plan(index_impl& ix, search_params const& sp, int m, int k) -> std::sha
                     std::to_string(dbg.stats) + std::to_string(dbg.taps) +
                     std::to_string(dbg.ordered_projection);
   std::lock_guard<std::mutex> lock(ix.mu);
-  auto it = ix.plans.find(key);
+  // one cached configuration: the previous buffers and graphs go before the new ones come
+  // (search.cu:807-812); a configuration has one plan per lane (see search_impl)
+  if (ix.plans.find(key) == ix.plans.end()) {
+    ix.plans.clear();
+    ix.plans[key] = make_plan(ix, sp, m, k, dbg);
+  }
+  if (lane == 0) return ix.plans[key];
+  const std::string other = key + "#" + std::to_string(lane);
+  auto it = ix.plans.find(other);
   if (it != ix.plans.end()) return it->second;
-  // one cached configuration: the previous buffers and graph go before the new ones come
-  // (search.cu:807-812)
-  ix.plans.clear();
-  auto pl       = make_plan(ix, sp, m, k, dbg);
-  ix.plans[key] = pl;
+  auto pl          = make_plan(ix, sp, m, k, dbg);
+  ix.plans[other]  = pl;
   return pl;
 }
 
@@ -534,13 +539,28 @@ void search_impl(resources const& res,
   cudaStream_t caller = res.stream;
   const int m         = static_cast<int>(std::min<int64_t>(std::max(sp.batch, 1), nq));
   auto pl             = get_plan(ix, sp, m, static_cast<int>(k));
-  std::lock_guard<std::mutex> lock(pl->mu);
-  const int D    = static_cast<int>(ix.dim);
-  auto& p        = ix.part;
-  cudaStream_t s = p.stream;
+  const int D = static_cast<int>(ix.dim);
+  auto& p     = ix.part;
+  // A call of several batches whose queries and results cross the bus alternates them between two
+  // lanes, each a plan (buffers and graph) on a stream of its own: the copies of one batch run
+  // under the kernels of the other. One lane when there is one batch, when the data is resident,
+  // when processes exchange inside the batch (their collectives are ordered on one stream), and
+  // when the plan keeps observations.
+  const bool two_lanes = !resident && pl->world == 1 && nq > m && !pl->dbg.stats && !pl->dbg.taps;
+  std::shared_ptr<plan> lane[2] = {pl, two_lanes ? get_plan(ix, sp, m, static_cast<int>(k), 1) : pl};
+  std::unique_lock<std::mutex> lock0(lane[0]->mu), lock1;
+  if (two_lanes) lock1 = std::unique_lock<std::mutex>(lane[1]->mu);
+  if (two_lanes && p.second == nullptr) {
+    OCTEX_CUDA_TRY(cudaSetDevice(p.device));
+    OCTEX_CUDA_TRY(cudaStreamCreateWithFlags(&p.second, cudaStreamNonBlocking));
+    OCTEX_CUDA_TRY(cudaSetDevice(cur));
+  }
+  cudaStream_t stream[2] = {p.stream, two_lanes ? p.second : p.stream};
+  const int lanes        = two_lanes ? 2 : 1;
   // a search with device outputs returns before its kernels ran; had one of them given up, the
   // word is still set and this is the first host code to see it
-  check_tc(*pl);
+  for (int l = 0; l < lanes; l++)
+    check_tc(*lane[l]);
 
   // the work of this call starts after what the caller queued on its stream (search.cu:841-848)
   // an event of the plan (one search at a time uses it: pl->mu), on the device of the caller's
@@ -554,52 +574,57 @@ void search_impl(resources const& res,
   cudaEvent_t start = pl->start_ev;
   OCTEX_CUDA_TRY(cudaEventRecord(start, caller));
   OCTEX_CUDA_TRY(cudaSetDevice(p.device));
-  OCTEX_CUDA_TRY(cudaStreamWaitEvent(s, start, 0));
-  for (int64_t b0 = 0; b0 < nq; b0 += m) {
-    const int n = static_cast<int>(std::min<int64_t>(m, nq - b0));
+  for (int l = 0; l < lanes; l++)
+    OCTEX_CUDA_TRY(cudaStreamWaitEvent(stream[l], start, 0));
+  int64_t batch = 0;
+  for (int64_t b0 = 0; b0 < nq; b0 += m, batch++) {
+    plan& w        = *lane[batch % lanes];
+    cudaStream_t s = stream[batch % lanes];
+    const int n    = static_cast<int>(std::min<int64_t>(m, nq - b0));
     if (!resident) {
       // rows [q1, q1 + m1) of the batch, the part beyond its end filled with copies of a row
       // (search.cu:870-883)
-      int have = std::clamp(n - pl->q1, 0, pl->m1);
+      int have = std::clamp(n - w.q1, 0, w.m1);
       if (have > 0) {
-        OCTEX_CUDA_TRY(cudaMemcpyAsync(pl->qbuf.ptr, queries + (b0 + pl->q1) * D,
-                                       sizeof(float) * have * D, cudaMemcpyDefault, s));
-      } else if (pl->m1 > 0) {
-        OCTEX_CUDA_TRY(cudaMemcpyAsync(pl->qbuf.ptr, queries + b0 * D, sizeof(float) * D,
+        OCTEX_CUDA_TRY(cudaMemcpyAsync(w.qbuf.ptr, queries + (b0 + w.q1) * D, sizeof(float) * have * D,
                                        cudaMemcpyDefault, s));
+      } else if (w.m1 > 0) {
+        OCTEX_CUDA_TRY(cudaMemcpyAsync(w.qbuf.ptr, queries + b0 * D, sizeof(float) * D, cudaMemcpyDefault, s));
         have = 1;
       }
-      if (have < pl->m1) kernels::pad_rows(pl->qbuf.as<float>(), have, pl->m1, D, s);
+      if (have < w.m1) kernels::pad_rows(w.qbuf.as<float>(), have, w.m1, D, s);
     }
-    if (sp.use_graph && pl->graph != nullptr)
-      OCTEX_CUDA_TRY(cudaGraphLaunch(pl->graph, s));
+    if (sp.use_graph && w.graph != nullptr)
+      OCTEX_CUDA_TRY(cudaGraphLaunch(w.graph, s));
     else
-      run_batch(ix, *pl, s, nullptr);  // use_graph = false, or a batch with exchanges
-    if (!resident && pl->world == 1) {
-      OCTEX_CUDA_TRY(cudaMemcpyAsync(neighbors + b0 * k, pl->bi, sizeof(int64_t) * n * k,
-                                     cudaMemcpyDefault, s));
-      OCTEX_CUDA_TRY(cudaMemcpyAsync(distances + b0 * k, pl->bd, sizeof(float) * n * k,
-                                     cudaMemcpyDefault, s));
+      run_batch(ix, w, s, nullptr);  // use_graph = false, or a batch with exchanges
+    if (!resident && w.world == 1) {
+      OCTEX_CUDA_TRY(cudaMemcpyAsync(neighbors + b0 * k, w.bi, sizeof(int64_t) * n * k, cudaMemcpyDefault, s));
+      OCTEX_CUDA_TRY(cudaMemcpyAsync(distances + b0 * k, w.bd, sizeof(float) * n * k, cudaMemcpyDefault, s));
     } else if (!resident) {
       // the gathered results: block r holds the rows [lo_r, hi_r) of the batch
-      for (int r = 0; r < pl->world; r++) {
-        const int lo_r = static_cast<int>(int64_t{m} * r / pl->world);
-        const int hi_r = static_cast<int>(int64_t{m} * (r + 1) / pl->world);
+      for (int r = 0; r < w.world; r++) {
+        const int lo_r = static_cast<int>(int64_t{m} * r / w.world);
+        const int hi_r = static_cast<int>(int64_t{m} * (r + 1) / w.world);
         const int rows = std::clamp(n - lo_r, 0, hi_r - lo_r);
         if (rows == 0) continue;
-        const char* block = pl->gathered.as<char>() + static_cast<size_t>(r) * pl->out_block;
+        const char* block = w.gathered.as<char>() + static_cast<size_t>(r) * w.out_block;
         OCTEX_CUDA_TRY(cudaMemcpyAsync(neighbors + (b0 + lo_r) * k, block, sizeof(int64_t) * rows * k,
                                        cudaMemcpyDefault, s));
-        OCTEX_CUDA_TRY(cudaMemcpyAsync(distances + (b0 + lo_r) * k, block + pl->out_ids,
-                                       sizeof(float) * rows * k, cudaMemcpyDefault, s));
+        OCTEX_CUDA_TRY(cudaMemcpyAsync(distances + (b0 + lo_r) * k, block + w.out_ids, sizeof(float) * rows * k,
+                                       cudaMemcpyDefault, s));
       }
     }
   }
-  OCTEX_CUDA_TRY(cudaEventRecord(pl->done_ev, s));
+  for (int l = 0; l < lanes; l++)
+    OCTEX_CUDA_TRY(cudaEventRecord(lane[l]->done_ev, stream[l]));
   OCTEX_CUDA_TRY(cudaSetDevice(cur));
-  OCTEX_CUDA_TRY(cudaStreamWaitEvent(caller, pl->done_ev, 0));
+  for (int l = 0; l < lanes; l++)
+    OCTEX_CUDA_TRY(cudaStreamWaitEvent(caller, lane[l]->done_ev, 0));
   if (host_out) OCTEX_CUDA_TRY(cudaStreamSynchronize(caller));
-  if (host_out) check_tc(*pl);
+  if (host_out)
+    for (int l = 0; l < lanes; l++)
+      check_tc(*lane[l]);
 }
 
 }  // namespace detail

@@ -75,6 +75,6 @@ auto profile_batch(resources const& res, search_params const& sp, index const& i
 /// report).
 void check_tc(plan const& pl);
 
-auto get_plan(index_impl& ix, search_params const& sp, int m, int k) -> std::shared_ptr<plan>;
+auto get_plan(index_impl& ix, search_params const& sp, int m, int k, int lane = 0) -> std::shared_ptr<plan>;
 
 }  // namespace octex_b200::detail

@@ -184,6 +184,36 @@ def test_batches_partial_and_empty(gpu_small):
     assert d3.shape == (0, 10) and i3.shape == (0, 10) and i3.dtype == np.int64 and d3.dtype == np.float32
 
 
+def test_batches_alternate_between_two_streams(gpu_wide):
+    """A call of several batches with host queries and nothing kept for inspection alternates its
+    batches between two plans on two streams (copies of one under the kernels of the other): the
+    same answers as one batch, for full and ragged batch counts, repeated, into caller's buffers,
+    and after work queued on a stream of the caller."""
+    import torch
+    idx, _, _, _, queries = gpu_wide
+    kw = dict(read=8, starts=32, waves=2, rerank=64, wave_rerank=64)
+    idx.set_debug(stats=False, taps=False)
+    try:
+        d0, i0 = idx.search(queries, 10, **kw)
+        for batch in (37, 64, 100, len(queries) // 2, len(queries) - 1):
+            for _ in range(3):
+                d1, i1 = idx.search(queries, 10, batch=batch, **kw)
+                assert np.array_equal(i0, i1) and np.array_equal(d0.view(np.uint32), d1.view(np.uint32)), batch
+        out_i = torch.zeros((len(queries), 10), dtype=torch.int64).pin_memory()
+        out_d = torch.zeros((len(queries), 10), dtype=torch.float32).pin_memory()
+        q_pin = torch.as_tensor(queries).pin_memory()
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            torch.empty(1 << 24, device="cuda").fill_(1.0)  # work ahead of the search on that stream
+            idx.search(q_pin.numpy(), 10, neighbors=out_i.numpy(), distances=out_d.numpy(), batch=50, **kw)
+        assert np.array_equal(out_i.numpy(), i0) and np.array_equal(out_d.numpy(), d0)
+        # back to one batch: the other plan and stream stay idle
+        d2, i2 = idx.search(queries, 10, **kw)
+        assert np.array_equal(i2, i0)
+    finally:
+        idx.set_debug(stats=True, taps=True)
+
+
 def test_torch_device_in_out(gpu_small):
     import torch
     idx, _, _, _, queries = gpu_small

@@ -1005,13 +1005,6 @@ __global__ void __launch_bounds__(kThreads, 1024 / kThreads) round_kernel(const 
               const int prev = atomicCAS(&table[s], -1, id);
               if (prev == -1) {
                 is_new = true;
-                // the sketch row of a new id will be wanted soon: start bringing it into L2
-                if (may_prefetch<kDealt>(a.sketch_map)) {
-                  if (a.keep_sketch)
-                    asm volatile("prefetch.global.L2::evict_last [%0];" ::"l"(a.sketch + static_cast<int64_t>(id) * S));
-                  else
-                    asm volatile("prefetch.global.L2 [%0];" ::"l"(a.sketch + static_cast<int64_t>(id) * S));
-                }
                 break;
               }
               if (prev == id) break;

@@ -88,7 +88,7 @@ LADDER = [
 # DRAM bytes (read + write) of one launch, from the ncu capture of this bench at its default workload
 # and the first rung of LADDER (profiles/round_kernel_descriptor-1m.md). Reported as
 # roofline.traffic only when the run uses exactly that workload and those parameters.
-NCU_TRAFFIC = {"round_rows": 1.181e9, "round_lists": 0.692e9}
+NCU_TRAFFIC = {"round_rows": 1.156e9, "round_lists": 0.651e9}
 
 
 def given_search(args):

@@ -55,7 +55,7 @@ struct round_layout {
     // constants (-2 alpha, sum of q^2); waves: the sketch-space query and the scales as floats
     qv     = take(a.sw);
     sc     = take(a.sw);
-    fq     = take(a.D);
+    fq     = take((a.D + 63) & ~63);  // in 64-element steps (query_slot)
     st     = take(a.nseg);
     len    = take(a.nseg);
     hist   = take(256);
@@ -586,7 +586,18 @@ __device__ __forceinline__ void sketch_rows_f32(const int* cand, int n, const si
   }
 }
 
-/// Rows j and j + stride of a lane group: squared distances of two fp16 rows to the query fq
+/// Where element i of the query sits in shared memory for exact_pair: within every step of 64
+/// elements the 16-byte chunks are dealt so that the eight lanes of a row group read consecutive
+/// chunks with each of their two loads (chunks 0, 2, 4, ... first, then 1, 3, 5, ...): one
+/// wavefront per load instead of two. The array takes the dimension rounded up to 64 floats.
+__device__ __forceinline__ int query_slot(int i)
+{
+  const int chunk = (i & 63) >> 2;
+  return (i & ~63) + ((((chunk & 1) << 3) + (chunk >> 1)) << 2) + (i & 3);
+}
+
+/// Rows j and j + stride of a lane group: squared distances of two fp16 rows to the query fq (laid
+/// out by query_slot)
 /// (shared memory, read 16 bytes at a time).
 /// Both row pointers are valid (a row that is not wanted is replaced by any row by the caller, who
 /// drops the result). kMode 0: any D that is a multiple of 8; 1: D a multiple of 128, so no step
@@ -615,8 +626,8 @@ __device__ __forceinline__ void exact_pair(const uint4* const (&row)[2], int Drt
     for (int s = 0; s < 2; s++) {
       const int hs = h0 + 64 * s;
       if (kWhole || hs < D) {
-        const float4 q0 = *reinterpret_cast<const float4*>(fq + hs);
-        const float4 q1 = *reinterpret_cast<const float4*>(fq + hs + 4);
+        const float4 q0 = *reinterpret_cast<const float4*>(fq + (hs - 8 * sub) + 4 * sub);
+        const float4 q1 = *reinterpret_cast<const float4*>(fq + (hs - 8 * sub) + 4 * sub + 32);
         const float qq[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
 #pragma unroll
         for (int u = 0; u < 2; u++) {
@@ -850,7 +861,7 @@ __global__ void __launch_bounds__(kThreads, 1024 / kThreads) round_kernel(const 
   }
   if (!a.sketch_rank)
     for (int i = threadIdx.x; i < a.D; i += blockDim.x)
-      fq[i] = a.Q[static_cast<int64_t>(q) * a.D + i];
+      fq[(a.D & 7) ? i : query_slot(i)] = a.Q[static_cast<int64_t>(q) * a.D + i];
   if (threadIdx.x == 0) ctrl[4] = 0;  // distinct ids
   // the kept list as the round finds it: read once, used by the start points, by the filter of
   // already kept ids and by the merge
@@ -1205,13 +1216,13 @@ __global__ void __launch_bounds__(kRoundThreads) final_rerank_kernel(const long 
   int* sid                   = reinterpret_cast<int*>(sorted + max(2 * P, 64));  // sorted [max(2 P, 64)]; sid [R]
   float* sdv                 = reinterpret_cast<float*>(sid + ((R + 3) & ~3));
   float* fq                  = sdv + ((R + 3) & ~3);                         // [D]
-  unsigned* hist             = reinterpret_cast<unsigned*>(fq + ((D + 3) & ~3));
+  unsigned* hist             = reinterpret_cast<unsigned*>(fq + ((D + 63) & ~63));
   int* wsum                  = reinterpret_cast<int*>(hist + 256);
   int* ctrl                  = wsum + 16;
   const int q                = blockIdx.x;
   const long long* ps        = si + static_cast<int64_t>(q) * KO;
   for (int i = threadIdx.x; i < D; i += blockDim.x)
-    fq[i] = Q[static_cast<int64_t>(q) * D + i];
+    fq[(D & 7) ? i : query_slot(i)] = Q[static_cast<int64_t>(q) * D + i];
   // the kept list is packed (valid entries first), so the valid ones among the first R are a prefix
   int mine = 0;
   for (int i = threadIdx.x; i < R; i += blockDim.x) {
@@ -1353,7 +1364,7 @@ void final_rerank(const long long* si, int KO, int R, const __half* vectors, row
   while (P < k)
     P <<= 1;
   const size_t words = 2 * static_cast<size_t>((k + R + 1) & ~1) + 2 * static_cast<size_t>(std::max(2 * P, 64)) +
-                       2 * static_cast<size_t>((R + 3) & ~3) + ((D + 3) & ~3) + 256 + 16 + 8;
+                       2 * static_cast<size_t>((R + 3) & ~3) + ((D + 63) & ~63) + 256 + 16 + 8;
   final_rerank_kernel<<<m, kRoundThreads, sizeof(int) * words, s>>>(si, KO, R, vectors, vector_map, D, Q,
                                                                     k, P, bi, bd, stats);
 }

@@ -557,11 +557,15 @@ __device__ __forceinline__ void sketch_rows_f32(const int* cand, int n, const si
   const int sub = lane % kLw, grp = lane / kLw;
   const bool live = 16 * sub < S;
   const int subc  = live ? sub : 0;
+  // the lane's sixteen scales and query values, 16 bytes at a time (both arrays start on 16-byte
+  // boundaries): a quarter of the shared-memory traffic of single words
   float cs[16], cq[16];
 #pragma unroll
-  for (int b = 0; b < 16; b++) {
-    cs[b] = live ? sc[sub * 16 + b] : 0.f;
-    cq[b] = live ? qv[sub * 16 + b] : 0.f;
+  for (int b = 0; b < 4; b++) {
+    const float4 s4 = live ? reinterpret_cast<const float4*>(sc + sub * 16)[b] : make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 q4 = live ? reinterpret_cast<const float4*>(qv + sub * 16)[b] : make_float4(0.f, 0.f, 0.f, 0.f);
+    cs[4 * b] = s4.x, cs[4 * b + 1] = s4.y, cs[4 * b + 2] = s4.z, cs[4 * b + 3] = s4.w;
+    cq[4 * b] = q4.x, cq[4 * b + 1] = q4.y, cq[4 * b + 2] = q4.z, cq[4 * b + 3] = q4.w;
   }
   const int rpp = nw * kG;  // rows per step of the block
   for (int jb = 0; jb < n; jb += 2 * rpp) {

@@ -49,7 +49,7 @@ WORKLOADS = {
     "embedding-1m": dict(
         gen="embedding_like", n=1_000_000, dim=96, nq=10_000,
         build=dict(copies=64, blocks=4, pca_dims=64, list_len=32, min_cell=16, log_buckets=20,
-                   sketch_width=64, table_len=64)),
+                   sketch_width=64, table_len=64)),  # the reference's rule gives 96: same recall, 30 % slower
     # BASELINE.json config 1: the index at the reference's defaults
     # (cpp/include/cuvs/neighbors/octex.hpp:32-92: 200 copies, lists of 64, 2^20 buckets, table of 64,
     # sketch width chosen from the dimension) and its stated search parameters, not retuned
@@ -524,7 +524,13 @@ def main():
     ids_run = dist_run = None
     fixed = [given_search(args)] if args.search else ([dict(w["search"])] if "search" in w else None)
     for sp in (fixed or LADDER[args.ladder_start:]):
-        d_, i_ = idx.search(q_dev, K, **sp)
+        try:
+            d_, i_ = idx.search(q_dev, K, **sp)
+        except ValueError as e:  # a rung beyond the limits of this index (starts x table_len)
+            if fixed:
+                raise
+            log(f"[rank {rank}] {sp} skipped: {e}")
+            continue
         r = recall_of(i_.cpu().numpy(), truth)
         log(f"[rank {rank}] {sp} recall@10 {r:.4f}")
         if r > rec:

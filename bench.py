@@ -426,8 +426,8 @@ def main():
     ap.add_argument("--workload", default="descriptor-1m", choices=sorted(WORKLOADS))
     ap.add_argument("--cpu-sample", type=int, default=2000)
     ap.add_argument("--ladder-start", type=int, default=0)
-    ap.add_argument("--e2e-batch", type=int, default=5000,
-                    help="queries per captured batch of the host-buffer call (search_params.batch)")
+    ap.add_argument("--e2e-batch", type=int, default=0,
+                    help="queries per captured batch of the host-buffer call (search_params.batch); 0: half the call")
     ap.add_argument("--builder", default="native", choices=["native", "torch"],
                     help="native: the library's own GPU builder writes the index directory (to "
                          "--index-dir) and the index is loaded from it; torch: the package's torch "
@@ -597,9 +597,11 @@ def main():
     e2e_one_s = host_call_seconds(0)
     ids_one_batch = on.copy()
     e2e_s, e2e_batch, e2e_split_s = e2e_one_s, 0, None
-    if not sharded and args.e2e_batch < nq:
-        # --e2e-batch and half of it: the slower the bus of the host, the finer the batches that pay
-        for b in (args.e2e_batch, max(args.e2e_batch // 2, 1)):
+    first = args.e2e_batch or nq // 2
+    if not sharded and 1 <= first < nq:
+        # half and a quarter of the call (or --e2e-batch and half of it): the slower the bus of the
+        # host, the finer the batches that pay
+        for b in (first, max(first // 2, 1)):
             t = host_call_seconds(b)
             if e2e_split_s is None or t < e2e_split_s[0]:
                 e2e_split_s = (t, b)

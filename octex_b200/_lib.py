@@ -92,7 +92,7 @@ SYMBOLS = (
     "octexB200SearchResident", "octexB200ProfileBatch", "octexB200SetDebug", "octexB200Fetch",
     "octexB200CellCodes", "octexB200QueryCodesStatic", "octexB200SetProjection",
     "octexB200CommUniqueId", "octexB200CommInit", "octexB200CommDisconnect", "octexB200CheckLast",
-    "octexB200MemoryReport", "octexB200Build", "octexB200ExactNeighbors",
+    "octexB200MemoryReport", "octexB200Build", "octexB200ExactNeighbors", "octexB200SetTable", "octexB200SearchedTable",
 )
 
 

@@ -18,7 +18,9 @@
 #include "npy.hpp"
 #include "sym_eigen.hpp"
 
+#include "index_impl.hpp"
 #include "kernels.hpp"
+#include "search_impl.hpp"
 
 #include <cub/cub.cuh>
 
@@ -680,15 +682,17 @@ __global__ void edge_bounds_kernel(const unsigned long long* __restrict__ key, i
   first[u] = lo;
 }
 
-// The half rule (build_table.cuh:529-554): a row's table is its first k/2 forward neighbors, then
-// up to k/2 nearest reverse edges, then the remaining forward ones; duplicates dropped (the first
-// occurrence stays), the first k kept, ordered nearest first (equal distances by id). One warp per
-// row; the candidates (at most k + k/2) sit in shared memory.
+// The reverse-edge rule (build_table.cuh:163-251,529-554): a row's table is its first kf forward
+// neighbors, then up to kr nearest reverse edges, then the remaining of its K forward ones;
+// duplicates dropped (the first occurrence stays), the first k kept, ordered nearest first (equal
+// distances by id). The exact table takes K = k, kf = kr = k / 2 (the half rule), the searched one
+// K = 3k / 2, kf = k / 4, kr = 3k / 4. One warp per row; the candidates (at most K + kr <= 256)
+// sit in shared memory.
 constexpr int kMergeMax = 256;
 __global__ void __launch_bounds__(128)
   half_rule_kernel(const int32_t* __restrict__ fwd, const float* __restrict__ fd, int K,
                    const unsigned long long* __restrict__ ekey, const int32_t* __restrict__ esrc,
-                   const int64_t* __restrict__ efirst, int64_t n, int k, int h, int32_t* __restrict__ table)
+                   const int64_t* __restrict__ efirst, int64_t n, int k, int kf, int kr, int32_t* __restrict__ table)
 {
   __shared__ int32_t cid[4][kMergeMax];
   __shared__ float cd[4][kMergeMax];
@@ -697,17 +701,17 @@ __global__ void __launch_bounds__(128)
   const int64_t v = static_cast<int64_t>(blockIdx.x) * 4 + warp;
   if (v >= n) return;
   const int64_t e0 = efirst[v], e1 = efirst[v + 1];
-  const int nrev   = static_cast<int>(min(e1 - e0, static_cast<int64_t>(h)));
-  const int total  = k + nrev;  // forward neighbors (self already dropped): k of them at most
+  const int nrev   = static_cast<int>(min(e1 - e0, static_cast<int64_t>(kr)));
+  const int total  = K + nrev;  // all K forward neighbors (self already dropped) and the reverse ones
   for (int t = lane; t < total; t += 32) {
     int32_t id;
     float d;
-    if (t < h) {
+    if (t < kf) {
       id = fwd[v * K + t];
       d  = fd[v * K + t];
-    } else if (t < h + nrev) {
-      id = esrc[e0 + (t - h)];
-      d  = __uint_as_float(static_cast<unsigned>(ekey[e0 + (t - h)] & 0xffffffffULL));
+    } else if (t < kf + nrev) {
+      id = esrc[e0 + (t - kf)];
+      d  = __uint_as_float(static_cast<unsigned>(ekey[e0 + (t - kf)] & 0xffffffffULL));
     } else {
       id = fwd[v * K + (t - nrev)];
       d  = fd[v * K + (t - nrev)];
@@ -788,6 +792,33 @@ void exact_neighbors(const __half* x, int64_t n, int D, int K, int method, int32
 
 namespace {
 
+// Reverse-edge merge of forward rows fwd / fd [n, K] (nearest first, -1 padded) into table rows
+// out [n, k]: every row v proposes itself to the rows among its first ks neighbors, a row takes its
+// first kf forward neighbors, up to kr nearest proposers, then its other forward neighbors
+// (half_rule_kernel). All pointers are device memory of `dev`.
+void reverse_merge(int dev, const int32_t* fwd, const float* fd, int64_t n, int K, int ks, int kf, int kr, int k,
+                   int32_t* out, cudaStream_t s)
+{
+  OCTEX_EXPECTS(K + kr <= kMergeMax && ks <= K && kf <= K && k <= K + kr, "octex: reverse merge: rows too long");
+  const int64_t edges = n * ks;
+  dbuf ekey(dev, 8 * edges), ekey_s(dev, 8 * edges), esrc(dev, 4 * edges), esrc_s(dev, 4 * edges),
+    efirst(dev, 8 * (n + 1));
+  reverse_edges_kernel<<<grid_for(edges, 256), 256, 0, s>>>(fwd, fd, n, K, ks, ekey.as<unsigned long long>(),
+                                                            esrc.as<int32_t>());
+  size_t tb = 0;
+  cub::DeviceRadixSort::SortPairs(nullptr, tb, ekey.as<unsigned long long>(), ekey_s.as<unsigned long long>(),
+                                  esrc.as<int32_t>(), esrc_s.as<int32_t>(), edges);
+  dbuf tmp(dev, tb);
+  cub::DeviceRadixSort::SortPairs(tmp.ptr, tb, ekey.as<unsigned long long>(), ekey_s.as<unsigned long long>(),
+                                  esrc.as<int32_t>(), esrc_s.as<int32_t>(), edges, 0, 64, s);
+  edge_bounds_kernel<<<grid_for(n + 1, 256), 256, 0, s>>>(ekey_s.as<unsigned long long>(), edges, n,
+                                                          efirst.as<int64_t>());
+  half_rule_kernel<<<grid_for(n, 4), 128, 0, s>>>(fwd, fd, K, ekey_s.as<unsigned long long>(), esrc_s.as<int32_t>(),
+                                                  efirst.as<int64_t>(), n, k, kf, kr, out);
+  OCTEX_CUDA_TRY(cudaPeekAtLastError());
+  OCTEX_CUDA_TRY(cudaStreamSynchronize(s));  // the scratch arrays go with this scope
+}
+
 // ---- the directory ---------------------------------------------------------------------------------
 
 /// A .npy file (format 1.0, little endian, C order, header padded to 64 bytes) written in pieces.
@@ -856,6 +887,98 @@ auto auto_sketch_width(int64_t dim) -> int
 {
   // build.cu:118-121 of the reference
   return static_cast<int>(std::max<int64_t>(std::min<int64_t>(dim / 16 * 16, 128), std::min<int64_t>(dim, 16)));
+}
+
+namespace {
+
+__global__ void rows_to_float_kernel(const __half* __restrict__ x, int64_t count, float* __restrict__ q)
+{
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < count) q[i] = __half2float(x[i]);
+}
+
+// The answers of a search of base rows [r0, r0 + m) for kq neighbors each, as forward rows of kin:
+// the row itself is dropped where it was found (else the last answer is).
+__global__ void forward_rows_kernel(const long long* __restrict__ ids, const float* __restrict__ dist, int64_t r0,
+                                    int64_t m, int kq, int kin, int32_t* __restrict__ fwd, float* __restrict__ fd)
+{
+  const int64_t r = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (r >= m) return;
+  int out = 0;
+  for (int t = 0; t < kq && out < kin; t++) {
+    const long long id = ids[r * kq + t];
+    if (id == r0 + r) continue;
+    fwd[(r0 + r) * kin + out] = id < 0 ? -1 : static_cast<int32_t>(id);
+    fd[(r0 + r) * kin + out]  = id < 0 ? INFINITY : dist[r * kq + t];
+    out++;
+  }
+  for (; out < kin; out++) {
+    fwd[(r0 + r) * kin + out] = -1;
+    fd[(r0 + r) * kin + out]  = INFINITY;
+  }
+}
+
+}  // namespace
+
+void searched_table(resources const& res, index& idx, int k, int passes, bool reverse_edges, int32_t* table_host,
+                    bool verbose)
+{
+  auto& ix = idx.impl();
+  auto& p  = ix.part;
+  OCTEX_EXPECTS(ix.world == 1, "octex: the searched table is made by one process");
+  OCTEX_EXPECTS(!p.vectors.host && !p.vector_rows.on, "octex: the searched table reads the fp16 rows from this GPU");
+  const int64_t n = ix.n;
+  const int D     = static_cast<int>(ix.dim);
+  // rows, passes and rule of build_table.cuh:586-614: forward rows of 3k/2 from a search for one
+  // more; a first round only, then 2 and 3 waves over the merged table of the pass before; a merged
+  // row keeps k/4 forward entries first and up to 3k/4 reverse ones
+  const int kin = k + k / 2, kq = kin + 1, kf = std::max(1, k / 4), kr = std::max(1, k - kf);
+  OCTEX_EXPECTS(k >= 1 && kq < n, "octex: table_len too large for the dataset");
+  OCTEX_EXPECTS(kq <= kernels::kMaxRerank, "octex: table_len too large for the searched table");
+  passes = std::clamp(passes, 1, 3);
+  const int pass_waves[3] = {0, 2, 3}, pass_starts[3] = {64, 128, 128};
+  int cur = 0;
+  OCTEX_CUDA_TRY(cudaGetDevice(&cur));
+  OCTEX_CUDA_TRY(cudaSetDevice(p.device));
+  cudaStream_t s = res.stream;
+  const int64_t chunk = std::min<int64_t>(n, 100000);
+  dbuf q(p.device, sizeof(float) * chunk * D), ids(p.device, sizeof(long long) * chunk * kq),
+    dist(p.device, sizeof(float) * chunk * kq), fwd(p.device, sizeof(int32_t) * n * kin),
+    fd(p.device, sizeof(float) * n * kin), merged(p.device, sizeof(int32_t) * n * k);
+  for (int v = 0; v < passes; v++) {
+    const auto t0 = std::chrono::steady_clock::now();
+    search_params sp;
+    sp.read         = std::min(64, ix.list_len);
+    sp.starts       = std::max(pass_starts[v], kq);
+    sp.waves        = ix.table_len > 0 ? pass_waves[v] : 0;
+    sp.batch        = 10000;
+    sp.sketch_rank  = true;
+    sp.final_rerank = kq;
+    for (int64_t r0 = 0; r0 < n; r0 += chunk) {
+      const int64_t m = std::min(chunk, n - r0);
+      OCTEX_CUDA_TRY(cudaStreamSynchronize(p.stream));  // the rows' owner stream, before this one reads them
+      rows_to_float_kernel<<<grid_for(m * D, 256), 256, 0, s>>>(p.vectors.as<__half>() + r0 * D, m * D, q.as<float>());
+      detail::search_impl(res, sp, idx, q.as<float>(), m, D, reinterpret_cast<int64_t*>(ids.ptr), dist.as<float>(), kq, false, false);
+      forward_rows_kernel<<<grid_for(m, 128), 128, 0, s>>>(ids.as<long long>(), dist.as<float>(), r0, m, kq, kin,
+                                                          fwd.as<int32_t>(), fd.as<float>());
+      OCTEX_CUDA_TRY(cudaPeekAtLastError());
+    }
+    OCTEX_CUDA_TRY(cudaStreamSynchronize(s));
+    if (reverse_edges) {
+      reverse_merge(p.device, fwd.as<int32_t>(), fd.as<float>(), n, kin, kin, kf, kr, k, merged.as<int32_t>(), s);
+    } else {
+      OCTEX_CUDA_TRY(cudaMemcpy2DAsync(merged.ptr, sizeof(int32_t) * k, fwd.ptr, sizeof(int32_t) * kin, sizeof(int32_t) * k,
+                                       n, cudaMemcpyDeviceToDevice, s));
+      OCTEX_CUDA_TRY(cudaStreamSynchronize(s));
+    }
+    detail::set_table(ix, merged.as<int32_t>(), k);
+    if (verbose)
+      std::fprintf(stderr, "octex: searched table, pass %d of %d (%d waves, %d starts): %.2f s\n", v + 1, passes,
+                   sp.waves, sp.starts, seconds_since(t0));
+  }
+  if (table_host != nullptr)
+    OCTEX_CUDA_TRY(cudaMemcpy(table_host, merged.ptr, merged.size, cudaMemcpyDeviceToHost));
+  OCTEX_CUDA_TRY(cudaSetDevice(cur));
 }
 
 void build(resources const& res, index_params const& given, build_dataset const& data, std::string const& path)
@@ -978,7 +1101,10 @@ void build(resources const& res, index_params const& given, build_dataset const&
   t0 = std::chrono::steady_clock::now();
   std::vector<int32_t> table;
   const int k = params.table_len;
-  if (k > 0) {
+  // above exact_table_max rows the table comes from the index's own search, once the rest of the
+  // directory is there (build_table.cuh:729-790)
+  const bool searched = k > 0 && n > params.exact_table_max;
+  if (k > 0 && !searched) {
     const int K = k;  // self is excluded inside the scan
     dbuf fwd(dev, sizeof(int32_t) * n * K), fd(dev, sizeof(float) * n * K);
     exact_neighbors(x16.as<__half>(), n, D, K, 0, fwd.as<int32_t>(), fd.as<float>(), s);
@@ -986,22 +1112,7 @@ void build(resources const& res, index_params const& given, build_dataset const&
     dbuf out(dev, sizeof(int32_t) * n * k);
     const int h = std::max(1, k / 2);
     if (params.reverse_edges) {
-      const int64_t edges = n * h;
-      dbuf ekey(dev, 8 * edges), ekey_s(dev, 8 * edges), esrc(dev, 4 * edges), esrc_s(dev, 4 * edges),
-        efirst(dev, 8 * (n + 1));
-      reverse_edges_kernel<<<grid_for(edges, 256), 256, 0, s>>>(fwd.as<int32_t>(), fd.as<float>(), n, K, h,
-                                                                ekey.as<unsigned long long>(), esrc.as<int32_t>());
-      size_t tb = 0;
-      cub::DeviceRadixSort::SortPairs(nullptr, tb, ekey.as<unsigned long long>(), ekey_s.as<unsigned long long>(),
-                                      esrc.as<int32_t>(), esrc_s.as<int32_t>(), edges);
-      dbuf tmp(dev, tb);
-      cub::DeviceRadixSort::SortPairs(tmp.ptr, tb, ekey.as<unsigned long long>(), ekey_s.as<unsigned long long>(),
-                                      esrc.as<int32_t>(), esrc_s.as<int32_t>(), edges, 0, 64, s);
-      edge_bounds_kernel<<<grid_for(n + 1, 256), 256, 0, s>>>(ekey_s.as<unsigned long long>(), edges, n,
-                                                              efirst.as<int64_t>());
-      half_rule_kernel<<<grid_for(n, 4), 128, 0, s>>>(fwd.as<int32_t>(), fd.as<float>(), K,
-                                                      ekey_s.as<unsigned long long>(), esrc_s.as<int32_t>(),
-                                                      efirst.as<int64_t>(), n, k, h, out.as<int32_t>());
+      reverse_merge(dev, fwd.as<int32_t>(), fd.as<float>(), n, K, h, h, h, k, out.as<int32_t>(), s);
       OCTEX_CUDA_TRY(cudaPeekAtLastError());
       table = to_host<int32_t>(out.ptr, static_cast<size_t>(n) * k);
     } else {
@@ -1058,9 +1169,9 @@ void build(resources const& res, index_params const& given, build_dataset const&
     auto hx = to_host<uint16_t>(x16.ptr, static_cast<size_t>(n) * D);
     write_array(path + "/vectors.npy", "<f2", {n, D}, hx.data());
   }
-  if (k > 0) write_array(path + "/table.npy", "<i4", {n, k}, table.data());
+  if (k > 0 && !searched) write_array(path + "/table.npy", "<i4", {n, k}, table.data());
   took.emplace_back("write", seconds_since(t0));
-  {
+  auto write_meta = [&](int table_len) {
     std::ofstream meta(path + "/meta.json", std::ios::trunc);
     OCTEX_EXPECTS(meta.good(), "octex: cannot write " + path + "/meta.json");
     meta << "{\"format\": 1, \"n\": " << n << ", \"dim\": " << D << ", \"copies\": " << C << ", \"blocks\": "
@@ -1068,13 +1179,32 @@ void build(resources const& res, index_params const& given, build_dataset const&
     for (int j = 0; j < L; j++)
       meta << (j ? ", " : "") << params.spacings[j];
     meta << "], \"list_len\": " << params.list_len << ", \"log_buckets\": " << params.log_buckets
-         << ", \"sketch_width\": " << S << ", \"table_len\": " << k << ", \"metric\": \"sqeuclidean\", \"build_seconds\": {";
+         << ", \"sketch_width\": " << S << ", \"table_len\": " << table_len << ", \"metric\": \"sqeuclidean\", \"build_seconds\": {";
     for (size_t i = 0; i < took.size(); i++)
       meta << (i ? ", " : "") << "\"" << took[i].first << "\": " << took[i].second;
     meta << "}}\n";
     meta.close();
     OCTEX_EXPECTS(meta.good(), "octex: writing " + path + "/meta.json failed");
+  };
+  if (!searched) {
+    write_meta(k);
+    return;
   }
+  // the directory without a table is complete and loadable; the searched table is added to it
+  write_meta(0);
+  t0 = std::chrono::steady_clock::now();
+  x16 = dbuf();  // the loaded index brings its own copy of the rows
+  {
+    load_params lp;
+    lp.devices = {dev};
+    lp.mode    = placement::replicate;
+    index idx  = load(res, path, lp);
+    table.assign(static_cast<size_t>(n) * k, -1);
+    searched_table(res, idx, k, params.table_passes, params.reverse_edges, table.data(), params.verbose);
+  }
+  write_array(path + "/table.npy", "<i4", {n, k}, table.data());
+  took.emplace_back("table_searched", seconds_since(t0));
+  write_meta(k);
 }
 
 }  // namespace octex_b200

@@ -37,4 +37,13 @@ inline void make_directory(std::string const& path)
 /// Returns after the stream has finished.
 void exact_neighbors(const __half* x, int64_t n, int D, int K, int method, int32_t* ids, float* dist, cudaStream_t s);
 
+/// The neighbor table of a loaded index by the index's own search (build_table.cuh:648-841 of the
+/// reference): every base row is searched for 3k/2 + 1 neighbors in passes — the first round alone,
+/// then 2 and 3 waves over the table of the pass before, ranking by sketch with an exact rerank at
+/// the end — the row itself is dropped and reverse edges are merged in (k/4 forward entries first,
+/// up to 3k/4 reverse ones). The index keeps the table of the last pass; table_host (may be null)
+/// int32 [n, k] receives it. One process, fp16 rows on its GPU.
+void searched_table(resources const& res, index& idx, int k, int passes, bool reverse_edges, int32_t* table_host,
+                    bool verbose);
+
 }  // namespace octex_b200

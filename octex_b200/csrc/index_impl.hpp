@@ -124,4 +124,9 @@ void connect_rows(index_impl& ix);
 /// Without it a process that closes early would free memory another still has mapped.
 void disconnect_rows(index_impl& ix);
 
+/// Replace the neighbor table of an index held by one process (load.cu:498-564 of the reference:
+/// set_table / drop_table): table int32 [n, table_len] in host or device memory is copied to the
+/// GPU of the index; table_len 0 (table may be null) drops the table. Plans made before are dropped.
+void set_table(index_impl& ix, const int32_t* table, int table_len);
+
 }  // namespace octex_b200::detail

@@ -398,6 +398,32 @@ void connect_rows(index_impl& ix)
   ix.plans.clear();  // plans made before the connection do not know the tables
 }
 
+void set_table(index_impl& ix, const int32_t* table, int table_len)
+{
+  OCTEX_EXPECTS(ix.world == 1, "octex: the table of an index shared by several processes cannot be replaced");
+  OCTEX_EXPECTS(table_len >= 0 && (table_len == 0 || table != nullptr), "octex: set_table needs a table");
+  auto& p = ix.part;
+  {
+    std::lock_guard<std::mutex> lock(ix.mu);
+    ix.plans.clear();
+  }
+  int cur = 0;
+  OCTEX_CUDA_TRY(cudaGetDevice(&cur));
+  OCTEX_CUDA_TRY(cudaSetDevice(p.device));
+  OCTEX_CUDA_TRY(cudaStreamSynchronize(p.stream));
+  if (!p.table.host) p.bytes -= static_cast<int64_t>(p.table.size);
+  p.table      = dbuf();
+  p.table_rows = dealt_rows{};
+  ix.table_len = table_len;
+  if (table_len > 0) {
+    p.table = dbuf(p.device, static_cast<size_t>(ix.n) * table_len * sizeof(int32_t));
+    p.bytes += static_cast<int64_t>(p.table.size);
+    OCTEX_CUDA_TRY(cudaMemcpyAsync(p.table.ptr, table, p.table.size, cudaMemcpyDefault, p.stream));
+    OCTEX_CUDA_TRY(cudaStreamSynchronize(p.stream));
+  }
+  OCTEX_CUDA_TRY(cudaSetDevice(cur));
+}
+
 void disconnect_rows(index_impl& ix)
 {
   auto& p = ix.part;

@@ -232,6 +232,32 @@ class Index:
         names = ("device", "copies", "sketch", "table", "vectors", "other", "buffers")
         return dict(zip(names, (int(v) for v in out)))
 
+    def set_table(self, table):
+        """Replace the neighbor table by ``table`` int32 [n, table_len] (numpy, or a torch tensor on
+        any device; copied), or drop it with ``None`` (``octexB200SetTable``).  One process only."""
+        if table is None:
+            _lib.check(_lib.lib().octexB200SetTable(self._h, None, C.c_int32(0)))
+            return
+        if _is_torch(table):
+            t = table.detach().to(_torch().int32).contiguous()
+            ptr, shape = t.data_ptr(), tuple(t.shape)
+        else:
+            t = np.ascontiguousarray(table, dtype=np.int32)
+            ptr, shape = t.ctypes.data, t.shape
+        if len(shape) != 2 or shape[0] != self.size:
+            raise ValueError("octex: the table must be [n, table_len]")
+        _lib.check(_lib.lib().octexB200SetTable(self._h, C.c_void_p(ptr), C.c_int32(shape[1])))
+
+    def searched_table(self, table_len=64, passes=3, reverse_edges=True):
+        """Make the neighbor table by this index's own search (``octexB200SearchedTable``: the
+        reference's table for more rows than ``exact_table_max``), keep it, and return it as a
+        numpy array int32 [n, table_len]."""
+        out = np.empty((self.size, int(table_len)), np.int32)
+        res = self._resources(0)
+        _lib.check(_lib.lib().octexB200SearchedTable(res.h, self._h, C.c_int32(int(table_len)), C.c_int32(int(passes)),
+                                                     C.c_int32(int(bool(reverse_edges))), C.c_void_p(out.ctypes.data)))
+        return out
+
     def save(self, path):
         """Copy the index directory to ``path`` (a new or empty directory); ``load(path)`` restores
         the index (octex/index.py:259-270 of the reference)."""

@@ -216,3 +216,53 @@ def test_tensor_core_neighbor_scan(n, dim, k):
     # both scans find the same rows but for near-ties
     same = np.mean([len(set(a.tolist()) & set(b.tolist())) / k for a, b in zip(ids_t, ids_p)])
     assert same > 0.999, same
+
+
+def test_searched_table(built, oracle, tmp_path):
+    """The table by the index's own search (octexB200SearchedTable; cuvsOctexBuild above
+    exact_table_max), the way the reference checks its own (cpp/tests/test_build.cu, table quality):
+    rows hold no repeats and not themselves, most of a row's true nearest neighbors are in it, a
+    search over it reaches the recall of the exact table, set_table(None) drops it."""
+    path, a, meta, base, queries = built
+    n, k = len(base), 24
+    idx = octex_b200.load(path, devices=[0], placement="replicate")
+    kw = dict(read=16, starts=64, waves=2, rerank=128, wave_rerank=128)
+    truth, _ = oracle.brute_force(a["vectors"].astype(np.float32), queries, 10)
+    _, ids_exact = idx.search(queries, 10, **kw)
+    table = idx.searched_table(table_len=k, passes=3)
+    assert table.shape == (n, k) and table.dtype == np.int32
+    rows = np.arange(0, n, 131)
+    x16 = a["vectors"].astype(np.float32)
+    near, _ = oracle.brute_force(x16, x16[rows], k // 2 + 1)
+    hit = first = 0
+    for t, v in enumerate(rows):
+        got = table[v][table[v] >= 0]
+        assert len(set(got.tolist())) == len(got) and v not in got
+        want = [i for i in near[t] if i != v][:k // 2]
+        hit += len(set(want) & set(got.tolist()))
+        first += len(set(want[:k // 4]) & set(got.tolist()))
+    # a row keeps its k / 4 nearest found neighbors first, reverse edges may displace later ones
+    # (the search of this six-copy index is approximate itself)
+    print(f"true nearest {k // 4} in the row: {first / (len(rows) * (k // 4)):.3f}, nearest {k // 2}: "
+          f"{hit / (len(rows) * (k // 2)):.3f}")
+    assert first / (len(rows) * (k // 4)) > 0.85
+    assert hit / (len(rows) * (k // 2)) > 0.7
+    _, ids_searched = idx.search(queries, 10, **kw)
+    r_exact, r_searched = recall(ids_exact, truth), recall(ids_searched, truth)
+    print(f"recall@10 exact table {r_exact:.4f}, searched table {r_searched:.4f}")
+    assert r_searched > r_exact - 0.02
+    idx.set_table(None)
+    _, ids_none = idx.search(queries, 10, read=16, starts=64, waves=0, rerank=128)
+    assert ids_none.shape == ids_exact.shape
+    idx.set_table(a["table"])
+    _, ids_back = idx.search(queries, 10, **kw)
+    assert np.array_equal(ids_back, ids_exact)
+    idx.close()
+    # the builder takes this way by itself above exact_table_max
+    small = base[:6000]
+    p2 = str(tmp_path / "searched")
+    octex_b200.build_native(small, p2, exact_table_max=1000, table_passes=2, **dict(PARAMS, copies=4))
+    m2 = json.load(open(os.path.join(p2, "meta.json")))
+    t2 = np.load(os.path.join(p2, "table.npy"))
+    assert m2["table_len"] == 24 and t2.shape == (6000, 24) and (t2[:, 0] >= 0).all()
+    assert "table_searched" in m2["build_seconds"]

@@ -185,12 +185,13 @@ OCTEX_B200_EXPORT cuvsError_t octexB200SetTable(cuvsOctexIndex_t index, const in
  * 3 table_len / 2 + 1 neighbors in `passes` passes (1 to 3: the first round alone, then 2 and 3 waves
  * over the table of the pass before), ranking by sketch with an exact rerank at the end; the row
  * itself is dropped and, unless reverse_edges is 0, reverse edges are merged in (table_len / 4
- * forward entries first, up to 3 table_len / 4 reverse ones). The index keeps the table of the last
+ * forward entries first, up to 3 table_len / 4 reverse ones). sketch_order non-zero leaves the
+ * answers in sketch order without the exact rerank (table_sketch_order). The index keeps the table of the last
  * pass; table (host memory, int32 [n, table_len], may be NULL) receives it. cuvsOctexBuild takes
  * this way by itself for more rows than exact_table_max. One process, fp16 rows on its GPU. */
 OCTEX_B200_EXPORT cuvsError_t octexB200SearchedTable(cuvsResources_t res, cuvsOctexIndex_t index,
                                                      int32_t table_len, int32_t passes, int32_t reverse_edges,
-                                                     int32_t* table);
+                                                     int32_t sketch_order, int32_t* table);
 
 /* Load an index directory onto the GPU of this process into an empty handle (params NULL: the
  * defaults). octex.h:268-271 */

@@ -52,9 +52,10 @@ struct search_params {
 
 /// octex.hpp:32-92. The builder of this library makes member lists (the rows of a cell nearest its
 /// centre first, the reference's member_lists mode) and a neighbor table that is exact up to
-/// exact_table_max rows and made by the index's own search in table_passes passes above that; the
-/// fields that choose among the reference's other build strategies (exact_lists, list_probes,
-/// member_lists, table_sketch_order, write_behind, devices) are accepted and have no effect.
+/// exact_table_max rows and made by the index's own search in table_passes passes above that
+/// (table_sketch_order: without the exact rerank of those searches); the fields that choose among
+/// the reference's other build strategies (exact_lists, list_probes, member_lists, write_behind,
+/// devices) are accepted and have no effect.
 struct index_params {
   int copies       = 200;   ///< random projections of the dataset
   int blocks       = 4;     ///< E8 blocks per copy (8 coordinates each)

@@ -920,8 +920,8 @@ __global__ void forward_rows_kernel(const long long* __restrict__ ids, const flo
 
 }  // namespace
 
-void searched_table(resources const& res, index& idx, int k, int passes, bool reverse_edges, int32_t* table_host,
-                    bool verbose)
+void searched_table(resources const& res, index& idx, int k, int passes, bool reverse_edges, bool sketch_order,
+                    int32_t* table_host, bool verbose)
 {
   auto& ix = idx.impl();
   auto& p  = ix.part;
@@ -953,7 +953,7 @@ void searched_table(resources const& res, index& idx, int k, int passes, bool re
     sp.waves        = ix.table_len > 0 ? pass_waves[v] : 0;
     sp.batch        = 10000;
     sp.sketch_rank  = true;
-    sp.final_rerank = kq;
+    sp.final_rerank = sketch_order ? 0 : kq;  // table_sketch_order: no exact rerank of the answers
     for (int64_t r0 = 0; r0 < n; r0 += chunk) {
       const int64_t m = std::min(chunk, n - r0);
       OCTEX_CUDA_TRY(cudaStreamSynchronize(p.stream));  // the rows' owner stream, before this one reads them
@@ -1200,7 +1200,8 @@ void build(resources const& res, index_params const& given, build_dataset const&
     lp.mode    = placement::replicate;
     index idx  = load(res, path, lp);
     table.assign(static_cast<size_t>(n) * k, -1);
-    searched_table(res, idx, k, params.table_passes, params.reverse_edges, table.data(), params.verbose);
+    searched_table(res, idx, k, params.table_passes, params.reverse_edges, params.table_sketch_order, table.data(),
+                   params.verbose);
   }
   write_array(path + "/table.npy", "<i4", {n, k}, table.data());
   took.emplace_back("table_searched", seconds_since(t0));

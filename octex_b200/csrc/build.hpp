@@ -41,9 +41,10 @@ void exact_neighbors(const __half* x, int64_t n, int D, int K, int method, int32
 /// reference): every base row is searched for 3k/2 + 1 neighbors in passes — the first round alone,
 /// then 2 and 3 waves over the table of the pass before, ranking by sketch with an exact rerank at
 /// the end — the row itself is dropped and reverse edges are merged in (k/4 forward entries first,
-/// up to 3k/4 reverse ones). The index keeps the table of the last pass; table_host (may be null)
-/// int32 [n, k] receives it. One process, fp16 rows on its GPU.
-void searched_table(resources const& res, index& idx, int k, int passes, bool reverse_edges, int32_t* table_host,
-                    bool verbose);
+/// up to 3k/4 reverse ones). sketch_order leaves the answers in sketch order without the exact
+/// rerank (index_params::table_sketch_order). The index keeps the table of the last pass;
+/// table_host (may be null) int32 [n, k] receives it. One process, fp16 rows on its GPU.
+void searched_table(resources const& res, index& idx, int k, int passes, bool reverse_edges, bool sketch_order,
+                    int32_t* table_host, bool verbose);
 
 }  // namespace octex_b200

@@ -363,6 +363,7 @@ cuvsError_t octexB200Build(cuvsResources_t res, cuvsOctexIndexParams_t params, c
     p.sketch_width = params->sketch_width, p.table_len = params->table_len;
     p.reverse_edges = params->reverse_edges, p.seed = params->seed;
     p.exact_table_max = params->exact_table_max, p.table_passes = params->table_passes;
+    p.table_sketch_order = params->table_sketch_order;
     p.verbose = verbose != 0;
     octex_b200::build_dataset d;
     d.data = dataset, d.f16 = f16 != 0, d.rows = rows, d.dim = dim;
@@ -494,10 +495,11 @@ cuvsError_t octexB200SetTable(cuvsOctexIndex_t index, const int32_t* table, int3
 }
 
 cuvsError_t octexB200SearchedTable(cuvsResources_t res, cuvsOctexIndex_t index, int32_t table_len, int32_t passes,
-                                   int32_t reverse_edges, int32_t* table)
+                                   int32_t reverse_edges, int32_t sketch_order, int32_t* table)
 {
   return translate([=] {
-    octex_b200::searched_table(as_res(res), *as_index(*index), table_len, passes, reverse_edges != 0, table, false);
+    octex_b200::searched_table(as_res(res), *as_index(*index), table_len, passes, reverse_edges != 0,
+                               sketch_order != 0, table, false);
   });
 }
 

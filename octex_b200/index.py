@@ -248,14 +248,15 @@ class Index:
             raise ValueError("octex: the table must be [n, table_len]")
         _lib.check(_lib.lib().octexB200SetTable(self._h, C.c_void_p(ptr), C.c_int32(shape[1])))
 
-    def searched_table(self, table_len=64, passes=3, reverse_edges=True):
+    def searched_table(self, table_len=64, passes=3, reverse_edges=True, sketch_order=False):
         """Make the neighbor table by this index's own search (``octexB200SearchedTable``: the
         reference's table for more rows than ``exact_table_max``), keep it, and return it as a
         numpy array int32 [n, table_len]."""
         out = np.empty((self.size, int(table_len)), np.int32)
         res = self._resources(0)
         _lib.check(_lib.lib().octexB200SearchedTable(res.h, self._h, C.c_int32(int(table_len)), C.c_int32(int(passes)),
-                                                     C.c_int32(int(bool(reverse_edges))), C.c_void_p(out.ctypes.data)))
+                                                     C.c_int32(int(bool(reverse_edges))), C.c_int32(int(bool(sketch_order))),
+                                                     C.c_void_p(out.ctypes.data)))
         return out
 
     def save(self, path):

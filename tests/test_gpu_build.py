@@ -251,6 +251,10 @@ def test_searched_table(built, oracle, tmp_path):
     r_exact, r_searched = recall(ids_exact, truth), recall(ids_searched, truth)
     print(f"recall@10 exact table {r_exact:.4f}, searched table {r_searched:.4f}")
     assert r_searched > r_exact - 0.02
+    # in sketch order (no exact rerank of the table's own searches): still a usable table
+    idx.searched_table(table_len=k, passes=2, sketch_order=True)
+    _, ids_sketch = idx.search(queries, 10, **kw)
+    assert recall(ids_sketch, truth) > r_exact - 0.05
     idx.set_table(None)
     _, ids_none = idx.search(queries, 10, read=16, starts=64, waves=0, rerank=128)
     assert ids_none.shape == ids_exact.shape

@@ -49,7 +49,8 @@ WORKLOADS = {
     "embedding-1m": dict(
         gen="embedding_like", n=1_000_000, dim=96, nq=10_000,
         build=dict(copies=64, blocks=4, pca_dims=64, list_len=32, min_cell=16, log_buckets=20,
-                   sketch_width=64, table_len=64)),  # the reference's rule gives 96: same recall, 30 % slower
+                   sketch_width=64, table_len=64,  # the reference's rule gives 96: same recall, 30 % slower
+                   exact_table_max=0)),  # the table by the index's own search: better recall here than the exact one
     # BASELINE.json config 1: the index at the reference's defaults
     # (cpp/include/cuvs/neighbors/octex.hpp:32-92: 200 copies, lists of 64, 2^20 buckets, table of 64,
     # sketch width chosen from the dimension) and its stated search parameters, not retuned
@@ -67,7 +68,7 @@ WORKLOADS = {
     "embedding-10m": dict(
         gen="embedding_like", n=10_000_000, dim=96, nq=10_000,
         build=dict(copies=64, blocks=4, pca_dims=64, list_len=32, min_cell=16, log_buckets=20,
-                   sketch_width=64, table_len=64)),
+                   sketch_width=64, table_len=64, exact_table_max=0)),
 }
 LADDER = [
     dict(read=16, starts=32, waves=1, rerank=128, wave_rerank=384),
@@ -89,6 +90,11 @@ LADDER = [
 # and the first rung of LADDER (profiles/round_kernel_descriptor-1m.md). Reported as
 # roofline.traffic only when the run uses exactly that workload and those parameters.
 NCU_TRAFFIC = {"round_rows": 1.156e9, "round_lists": 0.651e9}
+
+
+def torch_build(w):
+    """Build parameters the torch restatement of the builder knows (it always makes an exact table)."""
+    return {k_: v for k_, v in w["build"].items() if k_ not in ("exact_table_max", "table_passes")}
 
 
 def given_search(args):
@@ -288,7 +294,7 @@ def run_reference(args, rank, world):
         arrays, meta = index_dir.read_index(path)
     else:
         dev = "cuda" if torch.cuda.is_available() else "cpu"
-        arrays, meta = build_index.build_arrays(base, build_index.IndexParams(**w["build"]), device=dev)
+        arrays, meta = build_index.build_arrays(base, build_index.IndexParams(**torch_build(w)), device=dev)
     ox = oracle_py.Index(arrays, meta)
     sp = given_search(args) if args.search else dict(w.get("search", LADDER[args.ladder_start]))
     sample = queries[:args.cpu_sample]
@@ -437,6 +443,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-ref-kernels", action="store_true")
     ap.add_argument("--copies", type=int, default=0, help="override the copies of the build")
+    ap.add_argument("--table", default="", choices=["", "exact", "searched"],
+                    help="override how the build makes the neighbor table (index_params.exact_table_max)")
     ap.add_argument("--search", default="", help="JSON search parameters (skips the ladder)")
     ap.add_argument("--queries", type=int, default=0,
                     help="queries per batch instead of the workload's (small profiler captures)")
@@ -452,6 +460,8 @@ def main():
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if args.copies:
         WORKLOADS[args.workload]["build"]["copies"] = args.copies
+    if args.table:
+        WORKLOADS[args.workload]["build"]["exact_table_max"] = 0 if args.table == "searched" else 1 << 40
     if args.queries:
         WORKLOADS[args.workload]["nq"] = args.queries
     if args.impl == "reference":
@@ -499,7 +509,7 @@ def main():
         arrays = {"vectors": torch.as_tensor(np.asarray(host_arrays["vectors"]), device="cuda")}
         index_bytes = sum(int(v.nbytes) for v in host_arrays.values())
     else:
-        arrays, meta = build_index.build_arrays(base, build_index.IndexParams(**w["build"]),
+        arrays, meta = build_index.build_arrays(base, build_index.IndexParams(**torch_build(w)),
                                                 device=f"cuda:{local}", keep_on_device=True,
                                                 verbose=(rank == 0))
         torch.cuda.synchronize()
